@@ -1,0 +1,138 @@
+/*
+ * varq_b200 -- C ABI of the B200 (sm_100a) KV-cache quantization library.
+ *
+ * The reference project is pure Python and has no FFI of its own; every entry point
+ * below names the reference code it replaces (paths inside the reference project).
+ * All pointers are DEVICE pointers unless stated otherwise, all work is enqueued on
+ * the given CUDA stream (passed as void* = cudaStream_t), and nothing here
+ * synchronises the device.  Functions return VARQ_OK or a negative error code and
+ * never throw or trap; varq_last_error() gives the message of the calling thread's
+ * last failure.
+ *
+ * Logical tensor shape is always (B, L, H, D): batch, tokens, heads, head_dim.
+ * A tensor descriptor carries element strides for B, L and H; D is unit-stride.
+ * This covers the reference's 'BLHc' and 'BHLc' layouts (VAR_Q/quant.py:75-95) and
+ * the strided q/k/v views cut out of a fused QKV buffer
+ * (VAR/models/basic_var.py:123-135) without a staging copy.
+ */
+#ifndef VARQ_B200_H
+#define VARQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VARQ_OK                0
+#define VARQ_ERR_ARG          -1   /* null pointer, bad size, bad enum            */
+#define VARQ_ERR_UNSUPPORTED  -2   /* combination this build has no kernel for    */
+#define VARQ_ERR_CUDA         -3   /* launch or runtime failure                   */
+#define VARQ_ERR_WORKSPACE    -4   /* workspace missing or too small              */
+
+#define VARQ_F32  0
+#define VARQ_F16  1
+#define VARQ_BF16 2
+
+/* A (B, L, H, D) tensor whose last dim is contiguous.  Strides count elements of
+ * the tensor's own type (floats, halves, or int32 words for packed codes). */
+typedef struct {
+    void*   ptr;
+    int32_t dtype;          /* VARQ_F32 / F16 / BF16; ignored for packed codes */
+    int32_t _pad;
+    int64_t stride_b, stride_l, stride_h;
+} varq_tensor_t;
+
+/* Quantization parameters of a tensor or of a whole cache.
+ *
+ * A group is the set of elements that share one scale (and zero-point):
+ *   share_b / share_l / share_h = 1 : the group spans the whole batch / all tokens of
+ *   the call / all heads;  group = number of consecutive head_dim elements in it.
+ * The six reference modes (VAR_Q/quant.py:78-95) map to
+ *   G_TENSOR, G_SCALE            : share_b=share_l=share_h=1, group=D
+ *   G_SCALE_HEAD_DIM, G_HEAD_DIM : share_b=share_l=1, share_h=0, group=1
+ *   G_TOKEN                      : share_b=share_h=1, share_l=0, group=D
+ *   G_TOKEN_HEAD                 : share_b=1, share_l=share_h=0, group=D (or smaller)
+ * scale[i], zp[i] live at i = b*stride_b + row*stride_r + h*stride_h + (d/group)*stride_g
+ * with the stride of a shared dim ignored.  `row` is the token index, or
+ * row_of_token[token] when that table is given (modes whose parameters are constant
+ * over the tokens of one appended step keep one row per step).
+ * zp == NULL means symmetric quantization. */
+typedef struct {
+    float*         scale;
+    float*         zp;
+    const int32_t* row_of_token;
+    int64_t stride_b, stride_r, stride_h, stride_g;
+    int32_t share_b, share_l, share_h, group;
+} varq_qparams_t;
+
+/* Version string, static storage. */
+const char* varq_version(void);
+
+/* Message of the calling thread's last failed call (empty string if none). */
+const char* varq_last_error(void);
+
+/* Number of kernels this library has launched in the process so far (all threads).
+ * No counterpart in the reference; benchmarks use it to report their launch count. */
+uint64_t varq_launch_count(void);
+
+/* Pack int8 codes [n_rows, c] into int32 words [n_rows, ceil(c / (32/bits))]:
+ * value j of a word occupies bits [j*bits, (j+1)*bits), tail zero-padded.
+ * Replaces pack_last_dim_to_int32_triton / _python (VAR_Q/pack_unpack.py:107-134,
+ * 177-196) and the Triton kernel _pack2d_kernel (VAR_Q/pack_unpack.py:18-51). */
+int varq_pack_int8(const int8_t* codes, int64_t n_rows, int32_t c, int32_t bits,
+                   int32_t* words, void* stream);
+
+/* Inverse with sign extension.  Replaces unpack_last_dim_from_int32_triton / _python
+ * (VAR_Q/pack_unpack.py:136-162, 198-211) and _unpack2d_kernel (:54-88). */
+int varq_unpack_int8(const int32_t* words, int64_t n_rows, int32_t c, int32_t bits,
+                     int8_t* codes, void* stream);
+
+/* Bytes of scratch varq_quant_pack needs for this shape and grouping (0 if none). */
+size_t varq_quant_workspace_bytes(int32_t B, int32_t L, int32_t H, int32_t D,
+                                  int32_t x_dtype, int32_t store_bits,
+                                  const varq_qparams_t* grouping);
+
+/* Fused statistics -> scale (/zero-point) -> round -> clamp -> bit-pack of fresh K or V.
+ *   symmetric : scale = max(amax|x| / (2^(bits-1)-1), eps); q = clamp(rint(x/scale))
+ *   asymmetric: scale = max((max-min) / (2^bits-1), eps); zp = rint(-2^(bits-1) - min/scale);
+ *               q = clamp(rint(x/scale) + zp)
+ * all in fp32 with true division and round-half-even.  `bits` (2..8) sets the code
+ * range, `store_bits` (2, 4 or 8, >= bits) the packed field width.  Codes go to
+ * `codes` (int32 words, strides in words), parameters to p->scale / p->zp at row 0
+ * (offset the pointers to the row being written).
+ * Replaces VAR_Q._compute_scale, _quantize_to_int8 and _pack_last_dim_to_int32 as
+ * used by VAR_Q.quant (VAR_Q/quant.py:112-121, 127-131, 140-177). */
+int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D,
+                    int32_t bits, int32_t store_bits, float eps,
+                    const varq_tensor_t* codes, const varq_qparams_t* p,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Packed codes -> out = (code - zp) * scale, written as fp32, fp16 or bf16.
+ * Replaces VAR_Q._unpack_last_dim_from_int32 + _dequantize_from_int8 as used by
+ * dequant_current / dequant_all (VAR_Q/quant.py:123-124, 133-137, 208-224). */
+int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_t L, int32_t H, int32_t D,
+                        int32_t store_bits, const varq_qparams_t* p,
+                        const varq_tensor_t* out, void* stream);
+
+/* Bytes of scratch varq_attn_fwd needs (partial results of the key-split path). */
+size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
+                                 int32_t k_store_bits, int32_t v_store_bits);
+
+/* out = softmax(q k^T * softmax_scale) v over the packed cache, no mask, with
+ * k = (k_code - zp_k) * scale_k and v likewise, dequantised on the fly.
+ * q, out: (B, Lq, H, D) descriptors; k_codes, v_codes: (B, Lk, H, words) descriptors.
+ * Replaces dequant_all() followed by the attention consumer
+ * (VAR_Q/quant.py:216-224 + VAR/models/basic_var.py:156-162;
+ *  Infinity/infinity/models/basic.py:327-351). */
+int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_codes, const varq_tensor_t* v_codes,
+                  const varq_qparams_t* kp, const varq_qparams_t* vp,
+                  int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
+                  int32_t k_store_bits, int32_t v_store_bits, float softmax_scale,
+                  const varq_tensor_t* out, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VARQ_B200_H */

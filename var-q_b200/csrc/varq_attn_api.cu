@@ -1,0 +1,54 @@
+// C entry points of attention over the packed cache: argument checks and kernel selection.
+#include "varq_attn.cuh"
+
+using namespace varq;
+
+static bool words_aligned16(const varq_tensor_t* t, int words) {
+    return (words % 4 == 0) && aligned16(t->ptr) && (t->stride_b % 4 == 0) && (t->stride_l % 4 == 0) &&
+           (t->stride_h % 4 == 0);
+}
+
+extern "C" size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
+                                            int32_t k_store_bits, int32_t v_store_bits) {
+    (void)k_store_bits; (void)v_store_bits;
+    if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0 || D <= 0) return 0;
+    return attn_small_workspace_bytes(B, H, Lq, Lk, D);
+}
+
+extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_codes, const varq_tensor_t* v_codes,
+                             const varq_qparams_t* kp, const varq_qparams_t* vp, int32_t B, int32_t H, int32_t Lq,
+                             int32_t Lk, int32_t D, int32_t kb, int32_t vb, float softmax_scale,
+                             const varq_tensor_t* out, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!q || !k_codes || !v_codes || !kp || !vp || !out) return fail(VARQ_ERR_ARG, "varq_attn_fwd: null descriptor");
+    if ((kb != 2 && kb != 4 && kb != 8) || (vb != 2 && vb != 4 && vb != 8))
+        return fail(VARQ_ERR_ARG, "varq_attn_fwd: store bits must be 2, 4 or 8 (got %d, %d)", kb, vb);
+    if (B < 0 || H < 0 || Lq < 0 || Lk < 0 || D <= 0) return fail(VARQ_ERR_ARG, "varq_attn_fwd: bad shape");
+    if (!dtype_ok(q->dtype) || !dtype_ok(out->dtype)) return fail(VARQ_ERR_ARG, "varq_attn_fwd: bad q/out dtype");
+    if ((long long)B * H * Lq == 0) return VARQ_OK;
+    if (Lk == 0) return fail(VARQ_ERR_ARG, "varq_attn_fwd: empty cache (Lk = 0)");
+    if (!q->ptr || !out->ptr || !k_codes->ptr || !v_codes->ptr || !kp->scale || !vp->scale)
+        return fail(VARQ_ERR_ARG, "varq_attn_fwd: null pointer");
+    if (kp->group < 1 || kp->group > D || D % kp->group || vp->group < 1 || vp->group > D || D % vp->group)
+        return fail(VARQ_ERR_ARG, "varq_attn_fwd: group must divide head_dim");
+    const int kvw = 32 / kb, vvw = 32 / vb;
+    if (D % kvw || D % vvw || D % 4) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: head_dim %d must be a multiple of the codes per word (%d, %d)", D, kvw, vvw);
+    const int wk = D / kvw, wv = D / vvw;
+    if (wv > 128 || (128 % wv) != 0)
+        return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: V words per row (%d) must divide 128", wv);
+    if (D > 256) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: head_dim %d > 256", D);
+
+    AttnArgs a;
+    a.q = q->ptr; a.q_dtype = q->dtype; a.qs_b = q->stride_b; a.qs_l = q->stride_l; a.qs_h = q->stride_h;
+    a.out = out->ptr; a.o_dtype = out->dtype; a.os_b = out->stride_b; a.os_l = out->stride_l; a.os_h = out->stride_h;
+    a.kc = (const int32_t*)k_codes->ptr; a.ks_b = k_codes->stride_b; a.ks_l = k_codes->stride_l; a.ks_h = k_codes->stride_h;
+    a.vc = (const int32_t*)v_codes->ptr; a.vs_b = v_codes->stride_b; a.vs_l = v_codes->stride_l; a.vs_h = v_codes->stride_h;
+    a.kp = make_param_view(kp, false);
+    a.vp = make_param_view(vp, false);
+    a.B = B; a.H = H; a.Lq = Lq; a.Lk = Lk; a.D = D;
+    a.wk = wk; a.wv = wv; a.kpitch = wk;
+    a.k16 = words_aligned16(k_codes, wk);
+    a.v16 = words_aligned16(v_codes, wv);
+    a.scale_log2 = softmax_scale * 1.4426950408889634f;
+    a.splits = 1; a.tiles_per_split = 0; a.ws = nullptr;
+    return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
+}

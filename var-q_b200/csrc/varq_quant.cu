@@ -1,0 +1,499 @@
+// Fused quantize + pack of fresh K/V.
+//
+// Two device paths, both with one thread per packed int32 word (4 / 8 / 16 inputs):
+//   * rows path   - groups that keep (token, head) [per-token-per-head, optionally split
+//                   along head_dim and/or shared over the batch]: a CTA holds every member
+//                   of its groups in registers, so the input is read once;
+//   * tables path - any other grouping (per-dim, per-token, per-tensor ...): a statistics
+//                   kernel folds min/max into a small table with integer atomics on an
+//                   order-preserving encoding, a second kernel quantizes.
+// Arithmetic is fp32 with true division and round-half-even, the clamp after the round.
+#include "varq_common.cuh"
+
+namespace varq {
+
+struct QuantArgs {
+    const void* x;
+    long long xs_b, xs_l, xs_h;
+    int B, L, H, D;
+    int bits, symmetric, words;
+    float eps;
+    int32_t* codes;
+    long long cs_b, cs_l, cs_h;
+    float* scale;
+    float* zp;
+    long long ps_b, ps_r, ps_h, ps_g;   // strides of shared dims already zeroed
+    int share_b, share_l, share_h, group;
+    int nL, nH, nG;                     // statistics table dims ([nB, nL, nH, nG], 1 where shared)
+    uint32_t* stats;                    // [groups][2]: ord(max), ~ord(min)  (zero-initialised)
+};
+
+struct Range { uint32_t hi, lo; };      // hi = max f2ord(x or |x|), lo = max ~f2ord(x)
+
+__device__ __forceinline__ void range_init(Range& r) { r.hi = 0u; r.lo = 0u; }
+__device__ __forceinline__ void range_add(Range& r, float v, bool symmetric) {
+    if (symmetric) {
+        r.hi = max(r.hi, f2ord(fabsf(v)));
+    } else {
+        const uint32_t o = f2ord(v);
+        r.hi = max(r.hi, o);
+        r.lo = max(r.lo, ~o);
+    }
+}
+__device__ __forceinline__ void range_merge(Range& r, const Range& o) { r.hi = max(r.hi, o.hi); r.lo = max(r.lo, o.lo); }
+
+// scale / zero-point of a group from its range
+__device__ __forceinline__ void params_from_range(const Range& r, int bits, bool symmetric, float eps, float& scale,
+                                                  float& zp) {
+    if (symmetric) {
+        const float amax = ord2f(r.hi);
+        scale = fmaxf(__fdiv_rn(amax, (float)((1 << (bits - 1)) - 1)), eps);
+        zp = 0.0f;
+    } else {
+        const float mx = ord2f(r.hi), mn = ord2f(~r.lo);
+        scale = fmaxf(__fdiv_rn(__fsub_rn(mx, mn), (float)((1 << bits) - 1)), eps);
+        zp = __fadd_rn(rintf(__fsub_rn(-(float)(1 << (bits - 1)), __fdiv_rn(mn, scale))), 0.0f);
+    }
+}
+
+__device__ __forceinline__ int quantize_one(float x, float scale, float zp, bool symmetric, float bmin, float bmax) {
+    float r = rintf(__fdiv_rn(x, scale));
+    if (!symmetric) r = __fadd_rn(r, zp);
+    r = fminf(fmaxf(r, bmin), bmax);
+    return (int)r;
+}
+
+// =====================================================================================
+// rows path
+// =====================================================================================
+struct RowPlan {
+    int tpr;        // threads per (b, l, h) row = words per row
+    int bp;         // batch lanes per CTA (1 when the batch is not shared)
+    int ngr;        // group rows per pass
+    int nv;         // vectors per thread
+    int lpg;        // lanes per group = group / VPW
+    long long n_gr; // group rows in total: L*H (shared batch) or B*L*H
+    int h_fast;     // group-row enumeration: 1 = head index fastest
+};
+
+template <typename T, int STORE_BITS>
+__global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl) {
+    constexpr int VPW = 32 / STORE_BITS;
+    constexpr int NVMAX = 32 / VPW;
+    extern __shared__ uint32_t s_stats[];   // [ngr * groups_per_row][2], only when bp > 1
+
+    const int tid = threadIdx.x;
+    const int w = tid % pl.tpr;
+    const int rest = tid / pl.tpr;
+    const int g_local = rest % pl.ngr;
+    const int bl = rest / pl.ngr;
+    const bool sym = a.symmetric != 0;
+    const int d0 = w * VPW;
+    const int gpr = a.D / a.group;          // groups per row
+
+    if (pl.bp > 1) {
+        for (int i = tid; i < pl.ngr * gpr * 2; i += blockDim.x) s_stats[i] = 0u;
+        __syncthreads();
+    }
+
+    float v[NVMAX][VPW];
+    long long xoff[NVMAX];                   // element offset of the vector, -1 = not present
+    int vb[NVMAX], vl[NVMAX], vh[NVMAX];
+
+#pragma unroll
+    for (int k = 0; k < NVMAX; ++k) {
+        xoff[k] = -1;
+        if (k < pl.nv) {
+            long long gr;
+            int b;
+            if (a.share_b) { gr = (long long)blockIdx.x * pl.ngr + g_local; b = bl + k * pl.bp; }
+            else           { gr = ((long long)blockIdx.x * pl.nv + k) * pl.ngr + g_local; b = 0; }
+            if (gr < pl.n_gr && b < a.B) {
+                int l, h;
+                if (pl.h_fast) { h = (int)(gr % a.H); gr /= a.H; l = (int)(gr % a.L); gr /= a.L; }
+                else           { l = (int)(gr % a.L); gr /= a.L; h = (int)(gr % a.H); gr /= a.H; }
+                if (!a.share_b) b = (int)gr;
+                vb[k] = b; vl[k] = l; vh[k] = h;
+                xoff[k] = b * a.xs_b + l * a.xs_l + h * a.xs_h + d0;
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NVMAX; ++k)
+        if (xoff[k] >= 0) load_vals<T, VPW, true>(reinterpret_cast<const T*>(a.x) + xoff[k], v[k], VPW);
+
+    // ---- statistics
+    Range rg[NVMAX];
+#pragma unroll
+    for (int k = 0; k < NVMAX; ++k) {
+        range_init(rg[k]);
+        if (xoff[k] >= 0) {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) range_add(rg[k], v[k][j], sym);
+        }
+    }
+    if (a.share_b) {
+        // all vectors of a thread belong to one group: fold them, then across lanes, then across batch lanes
+#pragma unroll
+        for (int k = 1; k < NVMAX; ++k) range_merge(rg[0], rg[k]);
+        for (int m = 1; m < pl.lpg; m <<= 1) {
+            Range o;
+            o.hi = __shfl_xor_sync(0xffffffffu, rg[0].hi, m);
+            o.lo = __shfl_xor_sync(0xffffffffu, rg[0].lo, m);
+            range_merge(rg[0], o);
+        }
+        if (pl.bp > 1) {
+            const int slot = (g_local * gpr + d0 / a.group) * 2;
+            if ((w % pl.lpg) == 0) {
+                atomicMax(&s_stats[slot], rg[0].hi);
+                if (!sym) atomicMax(&s_stats[slot + 1], rg[0].lo);
+            }
+            __syncthreads();
+            rg[0].hi = s_stats[slot];
+            rg[0].lo = s_stats[slot + 1];
+        }
+#pragma unroll
+        for (int k = 1; k < NVMAX; ++k) rg[k] = rg[0];
+    } else {
+#pragma unroll
+        for (int k = 0; k < NVMAX; ++k) {
+            for (int m = 1; m < pl.lpg; m <<= 1) {
+                Range o;
+                o.hi = __shfl_xor_sync(0xffffffffu, rg[k].hi, m);
+                o.lo = __shfl_xor_sync(0xffffffffu, rg[k].lo, m);
+                range_merge(rg[k], o);
+            }
+        }
+    }
+
+    // ---- quantize, pack, store
+    const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
+    float scale = 0.f, zp = 0.f;
+    if (a.share_b) params_from_range(rg[0], a.bits, sym, a.eps, scale, zp);
+#pragma unroll
+    for (int k = 0; k < NVMAX; ++k) {
+        if (xoff[k] < 0) continue;
+        if (!a.share_b) params_from_range(rg[k], a.bits, sym, a.eps, scale, zp);
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) {
+            const int q = quantize_one(v[k][j], scale, zp, sym, bmin, bmax);
+            word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+        }
+        a.codes[vb[k] * a.cs_b + vl[k] * a.cs_l + vh[k] * a.cs_h + w] = (int32_t)word;
+        const bool writer = (d0 % a.group) == 0 && (a.share_b ? (vb[k] == 0) : true);
+        if (writer) {
+            const long long pi = vb[k] * a.ps_b + vl[k] * a.ps_r + vh[k] * a.ps_h + (long long)(d0 / a.group) * a.ps_g;
+            a.scale[pi] = scale;
+            if (!sym) a.zp[pi] = zp;
+        }
+    }
+}
+
+// =====================================================================================
+// tables path: blockDim = (TX column slots, TY rows); a column slot is one word of one head
+// =====================================================================================
+__device__ __forceinline__ long long group_id(const QuantArgs& a, int b, int l, int h, int d) {
+    const int bb = a.share_b ? 0 : b, ll = a.share_l ? 0 : l, hh = a.share_h ? 0 : h;
+    return (((long long)bb * a.nL + ll) * a.nH + hh) * a.nG + d / a.group;
+}
+
+__device__ __forceinline__ void stats_flush(uint32_t* stats, long long gid, const Range& r, bool sym) {
+    atomicMax(&stats[gid * 2], r.hi);
+    if (!sym) atomicMax(&stats[gid * 2 + 1], r.lo);
+}
+
+template <typename T, int STORE_BITS, bool VEC>
+__global__ void quant_stats_kernel(QuantArgs a, int iters) {
+    constexpr int VPW = 32 / STORE_BITS;
+    const int cs = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool col_ok = cs < a.H * a.words;
+    const int h = col_ok ? cs / a.words : 0, w = col_ok ? cs % a.words : 0;
+    const int d0 = w * VPW;
+    const int n_valid = min(VPW, a.D - d0);
+    const bool sym = a.symmetric != 0;
+    const bool uniform = (a.group % VPW) == 0;      // one group per thread-vector
+    const bool row_dep = !(a.share_b && a.share_l); // group depends on the (b, l) row
+    const long long R = (long long)a.B * a.L;
+    const long long r_step = (long long)gridDim.y * blockDim.y;
+
+    Range acc[VPW];
+#pragma unroll
+    for (int j = 0; j < VPW; ++j) range_init(acc[j]);
+
+    long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+    for (int it = 0; it < iters; ++it, r += r_step) {
+        const bool ok = col_ok && r < R;
+        int b = 0, l = 0;
+        if (ok) {
+            b = (int)(r / a.L); l = (int)(r % a.L);
+            float v[VPW];
+            load_vals<T, VPW, VEC>(reinterpret_cast<const T*>(a.x) + b * a.xs_b + l * a.xs_l + h * a.xs_h + d0, v, n_valid);
+            if (uniform) {
+#pragma unroll
+                for (int j = 0; j < VPW; ++j) if (j < n_valid) range_add(acc[0], v[j], sym);
+            } else {
+#pragma unroll
+                for (int j = 0; j < VPW; ++j) if (j < n_valid) range_add(acc[j], v[j], sym);
+            }
+        }
+        if (row_dep) {
+            if (uniform) {
+                // the whole warp often sits in one group (per-token statistics): fold it first
+                const long long gid = ok ? group_id(a, b, l, h, d0) : -1;
+                int same;
+                __match_all_sync(0xffffffffu, gid, &same);
+                if (same) {
+                    if (gid >= 0) {
+                        Range t;
+                        t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
+                        t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
+                        if ((threadIdx.y * blockDim.x + threadIdx.x) % 32 == 0) stats_flush(a.stats, gid, t, sym);
+                    }
+                } else if (ok) {
+                    stats_flush(a.stats, gid, acc[0], sym);
+                }
+                range_init(acc[0]);
+            } else if (ok) {
+#pragma unroll
+                for (int j = 0; j < VPW; ++j) {
+                    if (j < n_valid) stats_flush(a.stats, group_id(a, b, l, h, d0 + j), acc[j], sym);
+                    range_init(acc[j]);
+                }
+            }
+        }
+    }
+    if (!row_dep) {
+        if (uniform) {
+            const long long gid = col_ok ? group_id(a, 0, 0, h, d0) : -1;
+            int same;
+            __match_all_sync(0xffffffffu, gid, &same);
+            if (same) {
+                if (gid >= 0) {
+                    Range t;
+                    t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
+                    t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
+                    if ((threadIdx.y * blockDim.x + threadIdx.x) % 32 == 0) stats_flush(a.stats, gid, t, sym);
+                }
+            } else if (col_ok) {
+                stats_flush(a.stats, gid, acc[0], sym);
+            }
+        } else if (col_ok) {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j)
+                if (j < n_valid) stats_flush(a.stats, group_id(a, 0, 0, h, d0 + j), acc[j], sym);
+        }
+    }
+}
+
+template <typename T, int STORE_BITS, bool VEC>
+__global__ void quant_apply_kernel(QuantArgs a, int iters) {
+    constexpr int VPW = 32 / STORE_BITS;
+    const int cs = blockIdx.x * blockDim.x + threadIdx.x;
+    if (cs >= a.H * a.words) return;
+    const int h = cs / a.words, w = cs % a.words;
+    const int d0 = w * VPW;
+    const int n_valid = min(VPW, a.D - d0);
+    const bool sym = a.symmetric != 0;
+    const bool uniform = (a.group % VPW) == 0;
+    const bool row_dep = !(a.share_b && a.share_l);
+    const long long R = (long long)a.B * a.L;
+    const long long r_step = (long long)gridDim.y * blockDim.y;
+    const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
+    const int np = uniform ? 1 : VPW;
+
+    float scale[VPW], zp[VPW];
+    auto fetch = [&](int b, int l) {
+        for (int j = 0; j < np; ++j) {
+            const int d = min(d0 + j, a.D - 1);
+            const long long gid = group_id(a, b, l, h, d);
+            Range r;
+            r.hi = a.stats[gid * 2];
+            r.lo = a.stats[gid * 2 + 1];
+            params_from_range(r, a.bits, sym, a.eps, scale[j], zp[j]);
+        }
+    };
+    if (!row_dep) fetch(0, 0);
+
+    long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
+    for (int it = 0; it < iters && r < R; ++it, r += r_step) {
+        const int b = (int)(r / a.L), l = (int)(r % a.L);
+        if (row_dep) fetch(b, l);
+        float v[VPW];
+        load_vals<T, VPW, VEC>(reinterpret_cast<const T*>(a.x) + b * a.xs_b + l * a.xs_l + h * a.xs_h + d0, v, n_valid);
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) {
+            if (j < n_valid) {
+                const int pj = uniform ? 0 : j;
+                const int q = quantize_one(v[j], scale[pj], zp[pj], sym, bmin, bmax);
+                word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+            }
+        }
+        a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
+        // one writer per group: the member with the lowest shared coordinates
+        const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
+        if (first) {
+            for (int j = 0; j < np; ++j) {
+                const int d = d0 + j;
+                if (d < a.D && (d % a.group) == 0) {
+                    const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
+                    a.scale[pi] = scale[j];
+                    if (!sym) a.zp[pi] = zp[j];
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- host side
+static bool vec_ok(const varq_tensor_t* x, int D, int vpw) {
+    const int es = dtype_size(x->dtype);
+    const int chunk = (vpw * es) < 16 ? (vpw * es) : 16;
+    auto m = [&](long long s) { return ((s * es) % chunk) == 0; };
+    return (D % vpw == 0) && ((reinterpret_cast<uintptr_t>(x->ptr) % chunk) == 0) && m(x->stride_b) &&
+           m(x->stride_l) && m(x->stride_h);
+}
+
+static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+static bool plan_rows(const QuantArgs& a, int vpw, bool vec, RowPlan& pl, int& threads, size_t& smem) {
+    if (!vec || a.share_l || a.share_h) return false;
+    if (a.group % vpw != 0 || a.D % a.group != 0) return false;
+    pl.tpr = a.D / vpw;
+    pl.lpg = a.group / vpw;
+    if (!is_pow2(pl.tpr) || pl.tpr > 256 || !is_pow2(pl.lpg) || pl.lpg > 32) return false;
+    const int nvmax = 32 / vpw;
+    pl.h_fast = a.xs_h <= a.xs_l;
+    if (a.share_b) {
+        int bp = 1;
+        while (bp * nvmax < a.B) bp <<= 1;
+        if (pl.tpr * bp > 256) return false;
+        pl.bp = bp;
+        pl.nv = (a.B + bp - 1) / bp;
+        pl.ngr = 256 / (pl.tpr * bp);
+        if (pl.ngr < 1) pl.ngr = 1;
+        pl.n_gr = (long long)a.L * a.H;
+        threads = pl.tpr * pl.bp * pl.ngr;
+        smem = pl.bp > 1 ? (size_t)pl.ngr * (a.D / a.group) * 2 * sizeof(uint32_t) : 0;
+    } else {
+        pl.bp = 1;
+        pl.ngr = 256 / pl.tpr;
+        pl.nv = nvmax;
+        pl.n_gr = (long long)a.B * a.L * a.H;
+        threads = 256;
+        smem = 0;
+    }
+    return threads % 32 == 0 && threads <= 256;
+}
+
+template <typename T, int SB>
+static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes, cudaStream_t st) {
+    QuantArgs a = a0;
+    constexpr int VPW = 32 / SB;
+    RowPlan pl;
+    int threads = 0;
+    size_t smem = 0;
+    if (plan_rows(a, VPW, vec, pl, threads, smem) && threads >= 32) {
+        const long long per_cta = a.share_b ? pl.ngr : (long long)pl.ngr * pl.nv;
+        const long long blocks = (pl.n_gr + per_cta - 1) / per_cta;
+        if (blocks > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack: tensor too large");
+        quant_rows_kernel<T, SB><<<(unsigned)blocks, threads, smem, st>>>(a, pl);
+        VARQ_CUDA_TRY(cudaGetLastError());
+        count_launches(1);
+        return VARQ_OK;
+    }
+    // tables path
+    const long long groups = (long long)(a.share_b ? 1 : a.B) * a.nL * a.nH * a.nG;
+    const size_t need = (size_t)groups * 2 * sizeof(uint32_t);
+    if (!ws || ws_bytes < need)
+        return fail(VARQ_ERR_WORKSPACE, "varq_quant_pack: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+    a.stats = reinterpret_cast<uint32_t*>(ws);
+    VARQ_CUDA_TRY(cudaMemsetAsync(a.stats, 0, need, st));
+    const int cols = a.H * a.words;
+    int tx = 32;
+    while (tx < cols && tx < 256) tx <<= 1;
+    const int ty = 256 / tx;
+    const long long R = (long long)a.B * a.L;
+    const int gx = (cols + tx - 1) / tx;
+    long long gy = (R + ty - 1) / ty;
+    const long long cap = ((long long)sm_count() * 8 + gx - 1) / gx;   // ~8 CTAs of 256 threads per SM
+    if (gy > cap) gy = cap;
+    if (gy < 1) gy = 1;
+    if (gy > 65535) gy = 65535;
+    const int iters = (int)((R + gy * ty - 1) / (gy * ty));
+    dim3 block(tx, ty), grid(gx, (unsigned)gy);
+    if (vec) {
+        quant_stats_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
+        quant_apply_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
+    } else {
+        quant_stats_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
+        quant_apply_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
+    }
+    VARQ_CUDA_TRY(cudaGetLastError());
+    count_launches(2);
+    return VARQ_OK;
+}
+
+template <int SB>
+static int dispatch_quant(const QuantArgs& a, int dtype, bool vec, void* ws, size_t wsb, cudaStream_t st) {
+    switch (dtype) {
+        case VARQ_F32: return launch_quant<float, SB>(a, vec, ws, wsb, st);
+        case VARQ_F16: return launch_quant<__half, SB>(a, vec, ws, wsb, st);
+        default:       return launch_quant<__nv_bfloat16, SB>(a, vec, ws, wsb, st);
+    }
+}
+
+static int check_grouping(const char* fn, const varq_qparams_t* p, int D) {
+    if (!p) return fail(VARQ_ERR_ARG, "%s: null grouping", fn);
+    if (p->group < 1 || p->group > D) return fail(VARQ_ERR_ARG, "%s: group must be in [1, D] (got %d, D=%d)", fn, p->group, D);
+    if (D % p->group != 0) return fail(VARQ_ERR_ARG, "%s: head_dim %d is not a multiple of group %d", fn, D, p->group);
+    return VARQ_OK;
+}
+
+}  // namespace varq
+
+using namespace varq;
+
+extern "C" size_t varq_quant_workspace_bytes(int32_t B, int32_t L, int32_t H, int32_t D, int32_t x_dtype,
+                                             int32_t store_bits, const varq_qparams_t* g) {
+    (void)x_dtype; (void)store_bits;
+    if (!g || B <= 0 || L <= 0 || H <= 0 || D <= 0 || g->group < 1 || g->group > D) return 0;
+    // upper bound: the tables path may be taken for any grouping (unaligned input, large batch)
+    const long long groups = (long long)(g->share_b ? 1 : B) * (g->share_l ? 1 : L) * (g->share_h ? 1 : H) *
+                             ((D + g->group - 1) / g->group);
+    return (size_t)groups * 2 * sizeof(uint32_t);
+}
+
+extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D, int32_t bits,
+                               int32_t store_bits, float eps, const varq_tensor_t* codes, const varq_qparams_t* p,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !codes || !p) return fail(VARQ_ERR_ARG, "varq_quant_pack: null descriptor");
+    if (bits < 2 || bits > 8) return fail(VARQ_ERR_ARG, "varq_quant_pack: bits must be in [2, 8] (got %d)", bits);
+    if (store_bits != 2 && store_bits != 4 && store_bits != 8)
+        return fail(VARQ_ERR_ARG, "varq_quant_pack: store_bits must be 2, 4 or 8 (got %d)", store_bits);
+    if (store_bits < bits) return fail(VARQ_ERR_ARG, "varq_quant_pack: store_bits %d cannot hold %d-bit codes", store_bits, bits);
+    if (B < 0 || L < 0 || H < 0 || D <= 0) return fail(VARQ_ERR_ARG, "varq_quant_pack: bad shape (%d,%d,%d,%d)", B, L, H, D);
+    if (!dtype_ok(x->dtype)) return fail(VARQ_ERR_ARG, "varq_quant_pack: bad input dtype %d", x->dtype);
+    if (int rc = check_grouping("varq_quant_pack", p, D)) return rc;
+    if ((long long)B * L * H == 0) return VARQ_OK;
+    if (!x->ptr || !codes->ptr || !p->scale) return fail(VARQ_ERR_ARG, "varq_quant_pack: null pointer");
+
+    const int vpw = 32 / store_bits;
+    QuantArgs a;
+    a.x = x->ptr; a.xs_b = x->stride_b; a.xs_l = x->stride_l; a.xs_h = x->stride_h;
+    a.B = B; a.L = L; a.H = H; a.D = D;
+    a.bits = bits; a.symmetric = p->zp == nullptr; a.words = (D + vpw - 1) / vpw; a.eps = eps;
+    a.codes = (int32_t*)codes->ptr; a.cs_b = codes->stride_b; a.cs_l = codes->stride_l; a.cs_h = codes->stride_h;
+    a.scale = p->scale; a.zp = p->zp;
+    a.share_b = p->share_b != 0; a.share_l = p->share_l != 0; a.share_h = p->share_h != 0; a.group = p->group;
+    a.ps_b = a.share_b ? 0 : p->stride_b; a.ps_r = a.share_l ? 0 : p->stride_r;
+    a.ps_h = a.share_h ? 0 : p->stride_h; a.ps_g = p->stride_g;
+    a.nL = a.share_l ? 1 : L; a.nH = a.share_h ? 1 : H; a.nG = D / p->group;
+    a.stats = nullptr;
+    const bool vec = vec_ok(x, D, vpw);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (store_bits == 8) return dispatch_quant<8>(a, x->dtype, vec, workspace, workspace_bytes, st);
+    if (store_bits == 4) return dispatch_quant<4>(a, x->dtype, vec, workspace, workspace_bytes, st);
+    return dispatch_quant<2>(a, x->dtype, vec, workspace, workspace_bytes, st);
+}
