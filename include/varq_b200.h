@@ -109,6 +109,38 @@ int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int
                     const varq_tensor_t* codes, const varq_qparams_t* p,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* varq_quant_pack for callers that may not allocate device memory and have no scratch
+ * buffer to lend.  No counterpart in the reference.
+ *
+ * Who this is for: hosts where every byte of HBM already belongs to someone else's pool --
+ * an inference server that handed the whole device to its KV-cache allocator, a plugin
+ * loaded into an application that forbids cudaMalloc from plugin code -- and loops that
+ * cannot tolerate the device-wide synchronisation an allocation may cost.  Inputs and
+ * outputs are still the caller's; only the statistics table that the per-dim, per-token
+ * and per-tensor groupings need comes from a fixed array inside the library image.  This
+ * function and everything below it call no cudaMalloc / cudaFree and no allocating
+ * library routine.
+ *
+ * Limits and rules:
+ *  - the array holds 65536 groups (512 KiB, see varq_quant_static_scratch_bytes()); every
+ *    GPU that loads the library keeps it until the process exits.  A grouping with more
+ *    groups is refused with VARQ_ERR_WORKSPACE and a message naming both numbers;
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current).  Make that first call during
+ *    set-up, before any stream capture begins on that device;
+ *  - all calls on a device share the one array and it keeps the previous call's contents;
+ *    each call re-zeroes the part it uses on `stream` before accumulating.  Two calls
+ *    whose kernels can overlap on the GPU (different streams, or threads racing on one
+ *    device) corrupt each other's statistics: serialise them, or use varq_quant_pack
+ *    with separate workspaces.
+ * Results are bit-identical to varq_quant_pack. */
+int varq_quant_pack_static(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D,
+                           int32_t bits, int32_t store_bits, float eps,
+                           const varq_tensor_t* codes, const varq_qparams_t* p, void* stream);
+
+/* Size in bytes of the built-in scratch array used by varq_quant_pack_static. */
+size_t varq_quant_static_scratch_bytes(void);
+
 /* Packed codes -> out = (code - zp) * scale, written as fp32, fp16 or bf16.
  * Replaces VAR_Q._unpack_last_dim_from_int32 + _dequantize_from_int8 as used by
  * dequant_current / dequant_all (VAR_Q/quant.py:123-124, 133-137, 208-224). */

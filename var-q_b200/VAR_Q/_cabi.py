@@ -19,7 +19,8 @@ DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 # every symbol include/varq_b200.h declares
 SYMBOLS = (
     "varq_version", "varq_last_error", "varq_launch_count", "varq_pack_int8", "varq_unpack_int8",
-    "varq_quant_workspace_bytes", "varq_quant_pack", "varq_unpack_dequant",
+    "varq_quant_workspace_bytes", "varq_quant_pack", "varq_quant_pack_static",
+    "varq_quant_static_scratch_bytes", "varq_unpack_dequant",
     "varq_attn_workspace_bytes", "varq_attn_fwd",
 )
 
@@ -58,6 +59,10 @@ def _declare(lib):
     lib.varq_quant_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, Q]
     lib.varq_quant_pack.restype = i32
     lib.varq_quant_pack.argtypes = [T, i32, i32, i32, i32, i32, i32, f32, T, Q, vp, sz, vp]
+    lib.varq_quant_pack_static.restype = i32
+    lib.varq_quant_pack_static.argtypes = [T, i32, i32, i32, i32, i32, i32, f32, T, Q, vp]
+    lib.varq_quant_static_scratch_bytes.restype = sz
+    lib.varq_quant_static_scratch_bytes.argtypes = []
     lib.varq_unpack_dequant.restype = i32
     lib.varq_unpack_dequant.argtypes = [T, i32, i32, i32, i32, i32, Q, T, vp]
     lib.varq_attn_workspace_bytes.restype = sz

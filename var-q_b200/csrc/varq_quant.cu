@@ -497,3 +497,55 @@ extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int
     if (store_bits == 4) return dispatch_quant<4>(a, x->dtype, vec, workspace, workspace_bytes, st);
     return dispatch_quant<2>(a, x->dtype, vec, workspace, workspace_bytes, st);
 }
+
+// =====================================================================================
+// Quantize + pack without any allocation by the caller or by this library
+// =====================================================================================
+// Scratch for the statistics table of the tables path, resident in every GPU that loads the
+// library until the process exits.  Host code must not hand this name to a kernel: on the host
+// it is only a handle; the device address is looked up once per device below.
+#define VARQ_STATIC_SCRATCH_GROUPS 65536
+static __device__ __align__(256) uint32_t g_static_stats[VARQ_STATIC_SCRATCH_GROUPS * 2];
+
+namespace varq {
+static uint32_t* g_static_stats_addr[64] = {nullptr};   // per device ordinal, filled on first use
+
+// Device address of g_static_stats on the current device (looked up with that device current).
+static int static_scratch(uint32_t** out) {
+    int dev = -1;
+    VARQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack_static: device ordinal %d out of range", dev);
+    uint32_t* p = __atomic_load_n(&g_static_stats_addr[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        void* sym = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&sym, g_static_stats);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_stats)");
+        if (!sym) return fail(VARQ_ERR_CUDA, "varq_quant_pack_static: no device address for the built-in scratch");
+        p = reinterpret_cast<uint32_t*>(sym);
+        __atomic_store_n(&g_static_stats_addr[dev], p, __ATOMIC_RELEASE);   // same value from any thread
+    }
+    *out = p;
+    return VARQ_OK;
+}
+}  // namespace varq
+
+extern "C" size_t varq_quant_static_scratch_bytes(void) {
+    return (size_t)VARQ_STATIC_SCRATCH_GROUPS * 2 * sizeof(uint32_t);
+}
+
+extern "C" int varq_quant_pack_static(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D,
+                                      int32_t bits, int32_t store_bits, float eps, const varq_tensor_t* codes,
+                                      const varq_qparams_t* p, void* stream) {
+    if (!p) return fail(VARQ_ERR_ARG, "varq_quant_pack_static: null grouping");
+    const size_t have = varq_quant_static_scratch_bytes();
+    const size_t need = varq_quant_workspace_bytes(B, L, H, D, x ? x->dtype : VARQ_F32, store_bits, p);
+    if (need > have)
+        return fail(VARQ_ERR_WORKSPACE,
+                    "varq_quant_pack_static: this grouping has %zu groups but the built-in scratch holds %d; "
+                    "use varq_quant_pack with a caller-provided workspace",
+                    need / (2 * sizeof(uint32_t)), VARQ_STATIC_SCRATCH_GROUPS);
+    uint32_t* scratch = nullptr;
+    if (int rc = static_scratch(&scratch)) return rc;
+    // the statistics kernels clear the part of the table they use before accumulating into it
+    return varq_quant_pack(x, B, L, H, D, bits, store_bits, eps, codes, p, scratch, have, stream);
+}
