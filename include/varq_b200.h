@@ -77,6 +77,12 @@ const char* varq_last_error(void);
  * No counterpart in the reference; benchmarks use it to report their launch count. */
 uint64_t varq_launch_count(void);
 
+/* Every wait inside the kernels is bounded; a wait that expires makes the kernel record a
+ * non-zero code and drain instead of hanging.  This call synchronises with the device's prior
+ * work on the current device, returns the first such code since the last call (0 = none) and
+ * clears it.  HOST pointer.  No counterpart in the reference. */
+int varq_device_status(int32_t* status);
+
 /* Pack int8 codes [n_rows, c] into int32 words [n_rows, ceil(c / (32/bits))]:
  * value j of a word occupies bits [j*bits, (j+1)*bits), tail zero-padded.
  * Replaces pack_last_dim_to_int32_triton / _python (VAR_Q/pack_unpack.py:107-134,

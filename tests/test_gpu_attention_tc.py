@@ -1,0 +1,127 @@
+"""The tensor-core (tcgen05/TMEM) attention kernel, forced for every case, against the oracle
+and against the CUDA-core kernel.  Tolerance: max-abs 2e-3, relative L2 1e-3 (fp32 oracle)."""
+import os
+
+import pytest
+import torch
+
+from oracle import varq_oracle as O
+from VAR_Q import _cabi
+from VAR_Q.attention import attend_cached
+from VAR_Q.quant import VAR_Q
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _path_env():
+    old = os.environ.get("VARQ_ATTN_PATH")
+    yield
+    if old is None:
+        os.environ.pop("VARQ_ATTN_PATH", None)
+    else:
+        os.environ["VARQ_ATTN_PATH"] = old
+
+
+def run(path, q, kq, vq, scale, out_dtype=torch.float32):
+    os.environ["VARQ_ATTN_PATH"] = path
+    n0 = _cabi.lib().varq_launch_count()
+    out = attend_cached(q, kq, vq, scale, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0, "a kernel wait expired"
+    return out, _cabi.lib().varq_launch_count() - n0
+
+
+def make(fmt, B, H, steps, D, kb, vb, seed, mode="G_TOKEN_HEAD", **ext):
+    kq, vq = VAR_Q(kb, fmt, mode, **ext), VAR_Q(vb, fmt, mode, **ext)
+    kr, vr = O.OracleVARQ(kb, fmt, mode, **ext), O.OracleVARQ(vb, fmt, mode, **ext)
+    for si, n in enumerate(steps):
+        shape = (B, n, H, D) if fmt == "BLHc" else (B, H, n, D)
+        k = O.synthetic_kv(shape, fmt, seed + 2 * si, n_outlier=4)
+        v = O.synthetic_kv(shape, fmt, seed + 2 * si + 1, n_outlier=0)
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    return kq, vq, kd, vd
+
+
+def check(out, ref, tag):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    max_abs = (out - ref).abs().max().item()
+    rel = ((out - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+    assert max_abs <= 2e-3 and rel <= 1e-3, f"{tag}: max-abs {max_abs:.3e}, rel-L2 {rel:.3e}"
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("kb,vb", [(8, 8), (4, 4), (2, 2), (4, 2), (8, 2), (2, 8)])
+@pytest.mark.parametrize("symmetric", [True, False])
+def test_bit_widths(D, kb, vb, symmetric):
+    kq, vq, kd, vd = make("BHLc", 2, 3, (1, 4, 9, 16, 25, 36, 64, 100, 169, 256), D, kb, vb, seed=kb * 10 + vb, symmetric=symmetric)
+    q = torch.randn((2, 3, 256, D), generator=torch.Generator().manual_seed(D + kb))
+    out, launches = run("tc", q.to(DEV), kq, vq, 1.0 / D ** 0.5)
+    assert launches == 1
+    check(out, O.attention(q, kd, vd, "BHLc", 1.0 / D ** 0.5).transpose(1, 2), f"D={D} k{kb} v{vb} sym={symmetric}")
+
+
+@pytest.mark.parametrize("lq", [1, 9, 16, 100, 128, 129, 300])
+@pytest.mark.parametrize("lk", [1, 63, 64, 65, 127, 128, 129, 700])
+def test_ragged_tiles(lq, lk):
+    kq, vq, kd, vd = make("BLHc", 1, 2, (lk,), 64, 8, 4, seed=lq + lk)
+    q = torch.randn((1, lq, 2, 64), generator=torch.Generator().manual_seed(lq * 1000 + lk))
+    out, _ = run("tc", q.to(DEV), kq, vq, 0.125)
+    check(out, O.attention(q, kd, vd, "BLHc", 0.125), f"lq={lq} lk={lk}")
+    kq2, vq2, kd2, vd2 = make("BLHc", 1, 2, (lk,), 128, 4, 8, seed=lq + lk + 1)
+    q2 = torch.randn((1, lq, 2, 128), generator=torch.Generator().manual_seed(lq * 1000 + lk + 1))
+    out2, _ = run("tc", q2.to(DEV), kq2, vq2, 0.09)
+    check(out2, O.attention(q2, kd2, vd2, "BLHc", 0.09), f"D=128 lq={lq} lk={lk}")
+
+
+@pytest.mark.parametrize("q_dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("mode", ["G_TOKEN_HEAD", "G_TOKEN", "G_SCALE"])
+def test_query_dtypes_modes_and_agreement_with_cuda_core_kernel(q_dtype, mode):
+    kq, vq, kd, vd = make("BLHc", 2, 4, (30, 500, 470), 64, 8, 8, seed=3, mode=mode)
+    q = torch.randn((2, 200, 4, 64), generator=torch.Generator().manual_seed(5)).to(q_dtype)
+    tc, _ = run("tc", q.to(DEV), kq, vq, 0.125)
+    cc, _ = run("small", q.to(DEV), kq, vq, 0.125)
+    ref = O.attention(q, kd, vd, "BLHc", 0.125)
+    check(tc, ref, f"tc {mode} {q_dtype}")
+    check(cc, ref, f"small {mode} {q_dtype}")
+    check(tc, cc, "tc vs small")
+
+
+def test_large_logits_l2_normalised_keys():
+    # unit-norm K, queries scaled by 30 and 100: logits up to +-100, sharply peaked rows
+    fmt, B, H, D = "BLHc", 2, 2, 64
+    for gain in (30.0, 100.0):
+        kq, vq = VAR_Q(8, fmt, "G_TOKEN_HEAD"), VAR_Q(8, fmt, "G_TOKEN_HEAD")
+        kr, vr = O.OracleVARQ(8, fmt, "G_TOKEN_HEAD"), O.OracleVARQ(8, fmt, "G_TOKEN_HEAD")
+        k = torch.nn.functional.normalize(O.synthetic_kv((B, 680, H, D), fmt, 1), dim=-1)
+        v = O.synthetic_kv((B, 680, H, D), fmt, 2, n_outlier=0)
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        q = torch.nn.functional.normalize(torch.randn((B, 256, H, D), generator=torch.Generator().manual_seed(3)), dim=-1) * gain
+        out, _ = run("tc", q.to(DEV), kq, vq, 1.0)
+        check(out, O.attention(q, kr.use_var_q(k), vr.use_var_q(v), fmt, 1.0), f"gain {gain}")
+
+
+def test_full_size_last_scale_is_linear_in_v_and_permutation_invariant():
+    """VAR-d16 last scale (B2=64, H=16, Lq=256, Lk=680): too large for the CPU oracle in seconds.
+    Properties: (i) tensor-core and CUDA-core kernels agree; (ii) attention is invariant to a
+    permutation of the cached tokens (K and V permuted together)."""
+    B, H, Lq, Lk, D = 64, 16, 256, 680, 64
+    g = torch.Generator(device=DEV).manual_seed(0)
+    k = torch.nn.functional.normalize(torch.randn((B, Lk, H, D), generator=g, device=DEV), dim=-1)
+    v = torch.randn((B, Lk, H, D), generator=g, device=DEV)
+    q = torch.nn.functional.normalize(torch.randn((B, Lq, H, D), generator=g, device=DEV), dim=-1) * 4
+    def cached(kk, vv):
+        # per-sample statistics: the codes of a token do not depend on its position in the cache
+        a, b = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", reduce_batch=False), VAR_Q(8, "BLHc", "G_TOKEN_HEAD", reduce_batch=False)
+        a.append(kk); b.append(vv)
+        return a, b
+    kq, vq = cached(k, v)
+    tc, _ = run("tc", q, kq, vq, 1.0)
+    cc, _ = run("small", q, kq, vq, 1.0)
+    check(tc, cc, "tc vs small at full size")
+    perm = torch.randperm(Lk, generator=torch.Generator().manual_seed(1)).to(DEV)
+    kq2, vq2 = cached(k[:, perm].contiguous(), v[:, perm].contiguous())
+    tc2, _ = run("tc", q, kq2, vq2, 1.0)
+    check(tc2, tc, "token permutation")

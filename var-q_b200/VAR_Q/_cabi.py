@@ -18,7 +18,7 @@ DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 # every symbol include/varq_b200.h declares
 SYMBOLS = (
-    "varq_version", "varq_last_error", "varq_launch_count", "varq_pack_int8", "varq_unpack_int8",
+    "varq_version", "varq_last_error", "varq_launch_count", "varq_device_status", "varq_pack_int8", "varq_unpack_int8",
     "varq_quant_workspace_bytes", "varq_quant_pack", "varq_quant_pack_static",
     "varq_quant_static_scratch_bytes", "varq_unpack_dequant",
     "varq_attn_workspace_bytes", "varq_attn_fwd",
@@ -51,6 +51,8 @@ def _declare(lib):
     lib.varq_last_error.argtypes = []
     lib.varq_launch_count.restype = ctypes.c_uint64
     lib.varq_launch_count.argtypes = []
+    lib.varq_device_status.restype = i32
+    lib.varq_device_status.argtypes = [ctypes.POINTER(ctypes.c_int32)]
     lib.varq_pack_int8.restype = i32
     lib.varq_pack_int8.argtypes = [vp, i64, i32, i32, vp, vp]
     lib.varq_unpack_int8.restype = i32
@@ -120,3 +122,10 @@ def workspace(device, nbytes: int) -> torch.Tensor:
         buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+def device_status() -> int:
+    """First expired-wait code recorded by a kernel since the last call (0 = none); synchronises."""
+    out = ctypes.c_int32(0)
+    check(lib().varq_device_status(ctypes.byref(out)))
+    return int(out.value)

@@ -18,7 +18,50 @@ struct AttnArgs {
     float* ws;                  // partials: [(b,h,qtile,split)][QT*(2+D)]
 };
 
+__device__ __forceinline__ float load_q_elem(const void* q, int dtype, long long off) {
+    if (dtype == VARQ_F32) return __ldg(reinterpret_cast<const float*>(q) + off);
+    if (dtype == VARQ_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(q) + off));
+    return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(q) + off));
+}
+__device__ __forceinline__ void store_o_elem(void* o, int dtype, long long off, float v) {
+    if (dtype == VARQ_F32) reinterpret_cast<float*>(o)[off] = v;
+    else if (dtype == VARQ_F16) reinterpret_cast<__half*>(o)[off] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(o)[off] = __float2bfloat16_rn(v);
+}
+// 32 consecutive outputs starting at element `off`; 16-byte stores when the address allows
+__device__ __forceinline__ void store_o_row32(void* o, int dtype, long long off, const float (&v)[32]) {
+    const int es = dtype == VARQ_F32 ? 4 : 2;
+    const bool wide = (((reinterpret_cast<uintptr_t>(o) + (unsigned long long)off * es) & 15u) == 0);
+    if (!wide) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) store_o_elem(o, dtype, off + c, v[c]);
+    } else if (dtype == VARQ_F32) {
+        float4* p = reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + off);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) p[c] = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    } else {
+        uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(o) + off);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            uint4 raw;
+            if (dtype == VARQ_F16) {
+                __half* e = reinterpret_cast<__half*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = __float2half_rn(v[8 * c + j]);
+            } else {
+                __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(v[8 * c + j]);
+            }
+            p[c] = raw;
+        }
+    }
+}
+
 size_t attn_small_workspace_bytes(int B, int H, int Lq, int Lk, int D);
 int attn_small_run(AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
+bool attn_tc_eligible(const AttnArgs& a, int kb, int vb);
+int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st);
+int attn_tc_status(int* out);
 
 }  // namespace varq

@@ -1,4 +1,6 @@
 // C entry points of attention over the packed cache: argument checks and kernel selection.
+#include <cstdlib>
+
 #include "varq_attn.cuh"
 
 using namespace varq;
@@ -50,5 +52,17 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     a.v16 = words_aligned16(v_codes, wv);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.splits = 1; a.tiles_per_split = 0; a.ws = nullptr;
+    // small query counts stay on the CUDA-core kernel (memory-bound); the rest goes to the tensor cores
+    const char* force = getenv("VARQ_ATTN_PATH");       // "small" / "tc": testing aid, not a fallback switch
+    const bool want_tc = force ? (force[0] == 't') : (Lq > 8);
+    if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, (cudaStream_t)stream);
     return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int varq_device_status(int32_t* status) {
+    if (!status) return fail(VARQ_ERR_ARG, "varq_device_status: null pointer");
+    int v = 0;
+    if (int rc = attn_tc_status(&v)) return rc;
+    *status = v;
+    return VARQ_OK;
 }

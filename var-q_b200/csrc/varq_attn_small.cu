@@ -35,17 +35,6 @@ __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-__device__ __forceinline__ float load_q(const void* q, int dtype, long long off) {
-    if (dtype == VARQ_F32) return __ldg(reinterpret_cast<const float*>(q) + off);
-    if (dtype == VARQ_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(q) + off));
-    return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(q) + off));
-}
-__device__ __forceinline__ void store_o(void* o, int dtype, long long off, float v) {
-    if (dtype == VARQ_F32) reinterpret_cast<float*>(o)[off] = v;
-    else if (dtype == VARQ_F16) reinterpret_cast<__half*>(o)[off] = __float2half_rn(v);
-    else reinterpret_cast<__nv_bfloat16*>(o)[off] = __float2bfloat16_rn(v);
-}
-
 // stage `n` rows of `words` int32 each (row r at src + r*src_pitch) into dst rows of dst_pitch words
 __device__ __forceinline__ void stage_tile(uint32_t* dst, int dst_pitch, const int32_t* src, long long src_pitch,
                                            int n, int words, bool use16) {
@@ -88,7 +77,7 @@ __global__ void __launch_bounds__(A1_THREADS) attn_small_kernel(AttnArgs a) {
     for (int i = tid; i < QT * D; i += A1_THREADS) {
         const int qi = i / D, d = i - qi * D;
         float v = 0.f;
-        if (qi < nq) v = load_q(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + qi) * a.qs_l + h * a.qs_h + d) * a.scale_log2;
+        if (qi < nq) v = load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + qi) * a.qs_l + h * a.qs_h + d) * a.scale_log2;
         sQ[i] = v;
     }
     __syncthreads();
@@ -296,7 +285,7 @@ __global__ void __launch_bounds__(A1_THREADS) attn_small_kernel(AttnArgs a) {
 #pragma unroll
         for (int x = 0; x < QT; ++x) if (x == qi) { m = m_run[x]; l = l_run[x]; }
         if (a.splits == 1) {
-            store_o(a.out, a.o_dtype, b * a.os_b + (long long)(q0 + qi) * a.os_l + h * a.os_h + d, o / l);
+            store_o_elem(a.out, a.o_dtype, b * a.os_b + (long long)(q0 + qi) * a.os_l + h * a.os_h + d, o / l);
         } else {
             float* rec = a.ws + (((long long)bh * gridDim.y + qtile) * a.splits + split) * (QT * (2 + D));
             rec[QT * 2 + qi * D + d] = o;
@@ -326,7 +315,7 @@ __global__ void attn_small_merge_kernel(AttnArgs a, int n_qtiles) {
             num = fmaf(w, rec[QT * 2 + qi * a.D + d], num);
             den = fmaf(w, rec[QT + qi], den);
         }
-        store_o(a.out, a.o_dtype, b * a.os_b + (long long)qg * a.os_l + h * a.os_h + d, num / den);
+        store_o_elem(a.out, a.o_dtype, b * a.os_b + (long long)qg * a.os_l + h * a.os_h + d, num / den);
     }
 }
 

@@ -1,0 +1,518 @@
+// Attention over the packed cache on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Nine warps:
+//   warps 0-3  softmax: thread r owns query row r (TMEM lane r); reads S from TMEM, applies the
+//              per-key scale / zero-point of K, online softmax with lazy rescaling of O, writes
+//              P (fp16) to shared memory, final normalisation and store;
+//   warps 4-7  producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
+//              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
+//              K as exact fp16 integer codes, V as fp16 (code - zp) * scale;
+//   warp  8    one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
+//              O += P V, and commits completion to mbarriers.
+// Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
+// no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
+// rounded to fp16 (bf16 would miss the 1e-3 relative-L2 target by 10x).
+// Every wait is bounded: on expiry the kernel records a status code and all roles drain out.
+#include <cfloat>
+
+#include "varq_attn.cuh"
+
+namespace varq {
+
+constexpr int TC_THREADS = 288;
+constexpr int TC_M = 128;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
+
+__device__ int g_tc_status = 0;   // first failure code of any launch since the last read (0 = none)
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit expires or another thread has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (i > 32) __nanosleep(40);
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 format:
+// [0,14) start >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4 |
+// [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp16 A and B, fp32 accumulator.
+// [4,6) c format (1 = f32) | [7,10) a format (0 = f16) | [10,13) b format | 15 a major | 16 b major
+// (0 = K-major, 1 = MN-major) | [17,23) N >> 3 | [24,29) M >> 4
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, int b_mn_major) {
+    return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Byte offset of element (row, col) of a 128B-swizzled operand tile whose 64-column blocks hold
+// `rows` rows each (K-major A/B: row = M/N index, col = K index; MN-major B: row = K, col = N).
+__device__ __forceinline__ uint32_t tile_off(int row, int col, int rows) {
+    return (uint32_t)((col >> 6) * rows * 128 + (row >> 3) * 1024 + (row & 7) * 128 +
+                      ((((col & 63) >> 3) ^ (row & 7)) << 4) + ((col & 7) << 1));
+}
+
+// ---------------------------------------------------------------- shared-memory plan
+template <int D, int NQ> struct TcPlan {
+    static constexpr int N = (D == 64) ? 128 : 64;           // keys per tile
+    static constexpr int Q_BYTES = TC_M * D * 2;              // one fp16 Q tile
+    static constexpr int KV_BYTES = N * D * 2;                // one fp16 K (or V) tile
+    static constexpr int P_BYTES = TC_M * N * 2;
+    static constexpr int PK_BYTES = N * D;                    // packed staging at 8 bits (largest)
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = OFF_Q + NQ * Q_BYTES;        // [2]
+    static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;        // [2]
+    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [2]
+    static constexpr int OFF_PK = OFF_P + 2 * P_BYTES;        // [2][K, V]
+    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [2][2][N]: key scale, key zp*scale
+    static constexpr int OFF_BAR = OFF_KS + 2 * 2 * N * 4;    // mbarriers
+    static constexpr int N_BARS = 11;
+    static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
+    static constexpr int TOTAL = OFF_MISC + 16;
+    static constexpr int TMEM_COLS = (2 * N + D) <= 256 ? 256 : 512;
+    static constexpr int COL_S = 0, COL_O = 2 * N;
+};
+
+// Convert `BITS`-wide codes of one packed word to fp16 and write them to the operand tile.
+// EXACT: raw integer codes; otherwise (code - z) * s.
+template <int BITS, bool EXACT>
+__device__ __forceinline__ void put_word(unsigned char* tile, int key, int w, uint32_t word, int rows, float s, float z) {
+    constexpr int VPW = 32 / BITS;
+    __half h[VPW];
+#pragma unroll
+    for (int j = 0; j < VPW; ++j) {
+        const float c = (float)field<BITS>(word, j);
+        h[j] = __float2half_rn(EXACT ? c : (c - z) * s);
+    }
+    const int d0 = w * VPW;
+    if constexpr (VPW == 4) {
+        *reinterpret_cast<uint2*>(tile + tile_off(key, d0, rows)) = *reinterpret_cast<uint2*>(h);
+    } else {
+#pragma unroll
+        for (int c8 = 0; c8 < VPW / 8; ++c8)
+            *reinterpret_cast<uint4*>(tile + tile_off(key, d0 + 8 * c8, rows)) = *reinterpret_cast<uint4*>(h + 8 * c8);
+    }
+}
+
+template <int BITS, bool EXACT>
+__device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
+                                             int ptid, const ParamView& pv, int b, int h, int k0) {
+    constexpr int VPW = 32 / BITS;
+    const int total = N * W;
+    const int wshift = __ffs(W) - 1;          // W is a power of two
+    for (int idx = ptid; idx < total; idx += 128) {
+        const int key = idx >> wshift, w = idx & (W - 1);
+        uint32_t word = 0;
+        float s = 0.f, z = 0.f;
+        if (key < n_valid) {
+            word = packed[idx];
+            if constexpr (!EXACT) {
+                const long long pi = pv.index(b, pv.row(k0 + key), h, w * VPW);
+                s = __ldg(pv.scale + pi);
+                z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+            }
+        }
+        put_word<BITS, EXACT>(tile, key, w, word, N, s, z);
+    }
+}
+
+template <int D, int NQ>
+__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int kb, int vb) {
+    using P = TcPlan<D, NQ>;
+    constexpr int N = P::N;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
+    uint64_t* bar_pk = bars;          // [2] packed K+V rows landed (tx bytes)
+    uint64_t* bar_kv = bars + 2;      // [2] fp16 K/V operand tiles written (128 producers)
+    uint64_t* bar_s = bars + 4;       // [2] S = Q K^T complete (tcgen05.commit)
+    uint64_t* bar_p = bars + 6;       // [2] P written, O rescaled (128 softmax threads)
+    uint64_t* bar_pv = bars + 8;      // [2] O += P V complete (tcgen05.commit)
+    uint64_t* bar_o = bars + 10;      // all MMAs complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::OFF_MISC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh - b * a.H;
+    const int q0 = qt * TC_M;
+    const int nq = min(TC_M, a.Lq - q0);
+    const int T = (a.Lk + N - 1) / N;
+    const int wk = a.wk, wv = a.wv;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_pk[i], 1);
+            mbar_init(&bar_kv[i], 128);
+            mbar_init(&bar_s[i], 1);
+            mbar_init(&bar_p[i], 128);
+            mbar_init(&bar_pv[i], 1);
+        }
+        mbar_init(bar_o, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {   // TMEM allocation by one full warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // ---- Q tile -> shared (fp16 hi [, lo]), all threads
+    {
+        constexpr int CH = D / 8;   // 16-byte chunks per row
+        for (int i = tid; i < TC_M * CH; i += TC_THREADS) {
+            const int r = i / CH, c = i - r * CH;
+            __half hi[8], lo[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float v = 0.f;
+                if (r < nq) v = load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8 + j);
+                hi[j] = __float2half_rn(v);
+                lo[j] = __float2half_rn(v - __half2float(hi[j]));
+            }
+            const uint32_t off = tile_off(r, c * 8, TC_M);
+            *reinterpret_cast<uint4*>(smem + P::OFF_Q + off) = *reinterpret_cast<uint4*>(hi);
+            if constexpr (NQ == 2) *reinterpret_cast<uint4*>(smem + P::OFF_Q + P::Q_BYTES + off) = *reinterpret_cast<uint4*>(lo);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
+    const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
+
+    if (warp < 4) {
+        // =============================================================== softmax / epilogue
+        const int r = tid;                                  // query row = TMEM lane
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float qsum = 0.f;
+        if (a.kp.zp && r < nq) {
+            for (int d = 0; d < D; ++d) qsum += load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + d);
+        }
+        float m_used = -FLT_MAX, l_run = 0.f;
+        bool ok = true;
+        for (int j = 0; j < T && ok; ++j) {
+            const int buf = j & 1;
+            const int n_valid = min(N, a.Lk - j * N);
+            ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1, abort_flag, 10);          // per-key K parameters are visible
+            if (ok) ok = mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + buf * 2 * N;
+            const float* kz = ks + N;
+            float x[N];
+            float m_tile = -FLT_MAX;
+#pragma unroll
+            for (int c0 = 0; c0 < N; c0 += 32) {
+                uint32_t raw[32];
+                tmem_ld32(lane_base + P::COL_S + buf * N + c0, raw);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    float v = __uint_as_float(raw[c]) * ks[c0 + c] - kz[c0 + c] * qsum;
+                    v = (c0 + c < n_valid) ? v : -FLT_MAX;
+                    x[c0 + c] = v;
+                    m_tile = fmaxf(m_tile, v);
+                }
+            }
+            // lazy rescale: keep the running reference max until it is exceeded by more than 8 (log2 units)
+            float alpha = 1.f;
+            const bool need = m_tile > m_used + 8.f || j == 0;
+            if (need) {
+                alpha = (j == 0) ? 0.f : ex2(m_used - m_tile);
+                m_used = m_tile;
+            }
+            if (__any_sync(0xffffffffu, need) && j > 0) {
+                ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 12);   // O is stable
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t raw[32];
+                    tmem_ld32(lane_base + P::COL_O + c0, raw);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
+                    tmem_st32(lane_base + P::COL_O + c0, raw);
+                }
+                tmem_wait_st();
+            }
+            l_run *= alpha;
+            if (j >= 2) {   // the P buffer is free once the MMA that read it has completed
+                ok = mbar_wait(&bar_pv[buf], ((j - 2) >> 1) & 1, abort_flag, 13);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+            }
+            unsigned char* sp = smem + P::OFF_P + buf * P::P_BYTES;
+#pragma unroll
+            for (int c0 = 0; c0 < N; c0 += 8) {
+                __half ph[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    ph[c] = __float2half_rn(ex2(x[c0 + c] - m_used));
+                    l_run += __half2float(ph[c]);
+                }
+                *reinterpret_cast<uint4*>(sp + tile_off(r, c0, TC_M)) = *reinterpret_cast<uint4*>(ph);
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(&bar_p[buf]);
+        }
+        if (ok) ok = mbar_wait(bar_o, 0, abort_flag, 14);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / l_run;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t raw[32];
+                tmem_ld32(lane_base + P::COL_O + c0, raw);
+                tmem_wait_ld();
+                if (r < nq) {
+                    const long long off = b * a.os_b + (long long)(q0 + r) * a.os_l + h * a.os_h + c0;
+                    float v[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(raw[c]) * inv;
+                    store_o_row32(a.out, a.o_dtype, off, v);
+                }
+            }
+        }
+        tc_fence_before();
+    } else if (warp < 8) {
+        // =============================================================== producers
+        const int ptid = tid - 128;
+        auto issue = [&](int j) {
+            const int s = j & 1;
+            const int n_valid = min(N, a.Lk - j * N);
+            const uint32_t kbytes = (uint32_t)n_valid * wk * 4, vbytes = (uint32_t)n_valid * wv * 4;
+            mbar_expect_tx(&bar_pk[s], kbytes + vbytes);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)j * N * wk, kbytes, &bar_pk[s]);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, vbytes, &bar_pk[s]);
+        };
+        if (ptid == 0) {
+            issue(0);
+            if (T > 1) issue(1);
+        }
+        bool ok = true;
+        int issued = min(T, 2);
+        for (int j = 0; j < T; ++j) {
+            const int s = j & 1;
+            const int k0 = j * N;
+            const int n_valid = min(N, a.Lk - k0);
+            ok = mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
+            if (ok && j >= 2) ok = mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 22);   // operand stage is free
+            {   // all 128 producers take the same decision, so none is left alone at the barrier below
+                uint32_t all_ok;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+                ok = all_ok != 0;
+            }
+            if (!ok) break;
+            const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
+            const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
+            unsigned char* tk = smem + P::OFF_K + s * P::KV_BYTES;
+            unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
+            if (kb == 8) dequant_tile<8, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+            else if (kb == 4) dequant_tile<4, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+            else dequant_tile<2, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+            if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+            else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+            else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+            if (ptid < N) {   // per-key K parameters, pre-multiplied by softmax_scale * log2(e)
+                float* ks = reinterpret_cast<float*>(smem + P::OFF_KS) + s * 2 * N;
+                float sc = 0.f, zs = 0.f;
+                if (ptid < n_valid) {
+                    const long long pi = a.kp.index(b, a.kp.row(k0 + ptid), h, 0);
+                    sc = __ldg(a.kp.scale + pi) * a.scale_log2;
+                    zs = a.kp.zp ? __ldg(a.kp.zp + pi) * sc : 0.f;
+                }
+                ks[ptid] = sc;
+                ks[N + ptid] = zs;
+            }
+            fence_async_smem();
+            mbar_arrive(&bar_kv[s]);
+            asm volatile("bar.sync 1, 128;" ::: "memory");      // every producer is done with the packed stage
+            if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
+        }
+        if (!ok && ptid == 0) {
+            // drain: bulk copies already issued must land before the CTA may exit
+            for (int j = 0; j < issued; ++j) {
+                bool landed = false;
+                for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pk[j & 1], (j >> 1) & 1);
+            }
+        }
+    } else if (lane == 0) {
+        // =============================================================== MMA issue (one thread)
+        constexpr uint32_t IDESC_S = instr_desc(TC_M, N, 0);
+        constexpr uint32_t IDESC_O = instr_desc(TC_M, D, 1);
+        const uint32_t q_addr = smem_u32(smem + P::OFF_Q);
+        bool ok = true;
+        auto issue_pv = [&](int j) {
+            const int s = j & 1;
+            const uint32_t p_addr = smem_u32(smem + P::OFF_P + s * P::P_BYTES);
+            const uint32_t v_addr = smem_u32(smem + P::OFF_V + s * P::KV_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < N / 16; ++kk) {
+                const uint64_t ad = smem_desc(p_addr + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32, 16, 1024);
+                const uint64_t bd = smem_desc(v_addr + kk * 2048, N * 128, 1024);
+                tc_mma_f16(tmem_base + P::COL_O, ad, bd, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+            }
+            tc_commit(&bar_pv[s]);
+        };
+        for (int j = 0; j < T; ++j) {
+            const int s = j & 1;
+            ok = mbar_wait(&bar_kv[s], (j >> 1) & 1, abort_flag, 31);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t k_addr = smem_u32(smem + P::OFF_K + s * P::KV_BYTES);
+#pragma unroll
+            for (int qi = 0; qi < NQ; ++qi) {
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t ad = smem_desc(q_addr + qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32, 16, 1024);
+                    const uint64_t bd = smem_desc(k_addr + (kk >> 2) * (N * 128) + (kk & 3) * 32, 16, 1024);
+                    tc_mma_f16(tmem_base + P::COL_S + s * N, ad, bd, IDESC_S, (qi > 0 || kk > 0) ? 1u : 0u);
+                }
+            }
+            tc_commit(&bar_s[s]);
+            if (j >= 1) {
+                ok = mbar_wait(&bar_p[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 32);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(j - 1);
+            }
+        }
+        if (ok) {
+            ok = mbar_wait(&bar_p[(T - 1) & 1], ((T - 1) >> 1) & 1, abort_flag, 33);
+            if (ok) {
+                tc_fence_after();
+                issue_pv(T - 1);
+                tc_commit(bar_o);
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
+    if (a.D != 64 && a.D != 128) return false;
+    if (a.kp.group != a.D) return false;                       // K scale must be constant along head_dim
+    if ((a.wk & 3) || (a.wv & 3)) return false;                // 16-byte rows for the bulk copies
+    if (a.ks_l != a.wk || a.vs_l != a.wv) return false;        // tokens of one (sample, head) contiguous
+    if (!a.k16 || !a.v16) return false;
+    (void)kb; (void)vb;
+    return true;
+}
+
+template <int D, int NQ>
+static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
+    using P = TcPlan<D, NQ>;
+    static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
+    const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
+    VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int nqt = (a.Lq + TC_M - 1) / TC_M;
+    if ((long long)a.B * a.H > 65535) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: batch x heads > 65535");
+    dim3 grid(nqt, a.B * a.H);
+    attn_tc_kernel<D, NQ><<<grid, TC_THREADS, smem, st>>>(a, kb, vb);
+    VARQ_CUDA_TRY(cudaGetLastError());
+    count_launches(1);
+    return VARQ_OK;
+}
+
+int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
+    const bool split_q = a.q_dtype == VARQ_F32;    // fp16/bf16 queries are exact in one fp16 term
+    if (a.D == 64) return split_q ? launch_tc<64, 2>(a, kb, vb, st) : launch_tc<64, 1>(a, kb, vb, st);
+    return split_q ? launch_tc<128, 2>(a, kb, vb, st) : launch_tc<128, 1>(a, kb, vb, st);
+}
+
+int attn_tc_status(int* out) {
+    int v = 0;
+    VARQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        VARQ_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)));
+    }
+    *out = v;
+    return VARQ_OK;
+}
+
+}  // namespace varq
