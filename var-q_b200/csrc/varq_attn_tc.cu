@@ -134,14 +134,87 @@ template <int D, int NQ> struct TcPlan {
     static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;        // [2]
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [2]
     static constexpr int OFF_PK = OFF_P + 2 * P_BYTES;        // [2][K, V]
-    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [2][2][N]: key scale, key zp*scale
-    static constexpr int OFF_BAR = OFF_KS + 2 * 2 * N * 4;    // mbarriers
+    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [2][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
+    static constexpr int OFF_BAR = OFF_KS + 2 * 6 * N * 4;    // mbarriers
     static constexpr int N_BARS = 11;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
     static constexpr int TOTAL = OFF_MISC + 16;
     static constexpr int TMEM_COLS = (2 * N + D) <= 256 ? 256 : 512;
     static constexpr int COL_S = 0, COL_O = 2 * N;
 };
+
+
+// ---- packed integer codes -> fp16 without conversion instructions.
+// 0x6400 | u is the fp16 number 1024 + u (0 <= u < 1024); codes are biased to unsigned, placed in
+// the low byte of each half with byte permutes, and the bias is removed with one packed subtract.
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+// four unsigned bytes (each = code + bias) -> 4 halves holding the signed codes
+__device__ __forceinline__ void bytes_to_h4(uint32_t u, uint32_t bias_h2, uint32_t& h01, uint32_t& h23) {
+    h01 = h2_sub(__byte_perm(u, 0x64646464u, 0x4140), bias_h2);
+    h23 = h2_sub(__byte_perm(u, 0x64646464u, 0x4342), bias_h2);
+}
+template <int BITS> struct Codes;
+template <> struct Codes<8> {   // one word -> 4 halves
+    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
+        bytes_to_h4(w ^ 0x80808080u, 0x64806480u, h[0], h[1]);           // 1024 + 128 + c
+    }
+};
+template <> struct Codes<4> {   // one word -> 8 halves
+    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
+        const uint32_t x = w ^ 0x88888888u;                               // c + 8 per nibble
+        const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu; // fields 0,2,4,6 / 1,3,5,7
+        bytes_to_h4(__byte_perm(lo, hi, 0x5140), 0x64086408u, h[0], h[1]);
+        bytes_to_h4(__byte_perm(lo, hi, 0x7362), 0x64086408u, h[2], h[3]);
+    }
+};
+template <> struct Codes<2> {   // one word -> 16 halves
+    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
+        const uint32_t x = w ^ 0xAAAAAAAAu;                               // c + 2 per field
+        const uint32_t t0 = x & 0x03030303u, t1 = (x >> 2) & 0x03030303u; // fields 0,4,8,12 / 1,5,9,13
+        const uint32_t t2 = (x >> 4) & 0x03030303u, t3 = (x >> 6) & 0x03030303u;
+        const uint32_t a = __byte_perm(t0, t1, 0x5140), b = __byte_perm(t2, t3, 0x5140);   // f0 f1 f4 f5 / f2 f3 f6 f7
+        const uint32_t c = __byte_perm(t0, t1, 0x7362), d = __byte_perm(t2, t3, 0x7362);   // f8 f9 f12 f13 / f10 f11 f14 f15
+        bytes_to_h4(__byte_perm(a, b, 0x5410), 0x64026402u, h[0], h[1]);
+        bytes_to_h4(__byte_perm(a, b, 0x7632), 0x64026402u, h[2], h[3]);
+        bytes_to_h4(__byte_perm(c, d, 0x5410), 0x64026402u, h[4], h[5]);
+        bytes_to_h4(__byte_perm(c, d, 0x7632), 0x64026402u, h[6], h[7]);
+    }
+};
+
+// Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
+template <int BITS>
+__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid) {
+    constexpr int VPW = 32 / BITS;            // codes per word
+    constexpr int HW = VPW / 2;               // 32-bit half2 registers per word
+    const int ipr = W >> 2;                   // 16-byte items per key row
+    const int ishift = __ffs(ipr) - 1;
+    const int items = N * ipr;
+#pragma unroll 2
+    for (int it = ptid; it < items; it += 128) {
+        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+        uint4 pk = make_uint4(0u, 0u, 0u, 0u);
+        uint32_t h[4 * HW];
+        if (key < n_valid) {
+            pk = *reinterpret_cast<const uint4*>(packed + key * W + wi);
+            Codes<BITS>::cvt(pk.x, h);
+            Codes<BITS>::cvt(pk.y, h + HW);
+            Codes<BITS>::cvt(pk.z, h + 2 * HW);
+            Codes<BITS>::cvt(pk.w, h + 3 * HW);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+        }
+        const int d0 = wi * VPW;              // first head_dim index of the item
+        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
+        const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+        for (int c = 0; c < HW; ++c)         // HW chunks of 8 halves
+            *reinterpret_cast<uint4*>(row + (((ch0 + c) ^ (key & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+    }
+}
 
 // Convert `BITS`-wide codes of one packed word to fp16 and write them to the operand tile.
 // EXACT: raw integer codes; otherwise (code - z) * s.
@@ -183,6 +256,41 @@ __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t
             }
         }
         put_word<BITS, EXACT>(tile, key, w, word, N, s, z);
+    }
+}
+
+// ---- softmax over 32 columns of S held in registers.  Per-key tables (shared memory):
+// ks = K scale * softmax_scale * log2(e) (0 past the end), b1 = 0 / -1e30 mask bias,
+// b2 = b1 + log2(V scale), kzs = K zero-point * ks, vinv = 1 / V scale, vz = V zero-point.
+template <bool KZ>
+__device__ __forceinline__ float softmax_max32(const uint32_t (&raw)[32], const float* ks, const float* b1,
+                                               const float* kzs, float qsum, float m) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+        float v = fmaf(__uint_as_float(raw[c]), ks[c], b1[c]);
+        if (KZ) v = fmaf(-kzs[c], qsum, v);
+        m = fmaxf(m, v);
+    }
+    return m;
+}
+template <bool KZ, bool VX, bool VZ>
+__device__ __forceinline__ void softmax_exp32(const uint32_t (&raw)[32], uint32_t (&ph)[16], const float* ks,
+                                              const float* b2, const float* kzs, const float* vinv, const float* vz,
+                                              float qsum, float m_used, float& l_run, float& corr) {
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+        float x0 = fmaf(__uint_as_float(raw[c]), ks[c], b2[c]);
+        float x1 = fmaf(__uint_as_float(raw[c + 1]), ks[c + 1], b2[c + 1]);
+        if (KZ) { x0 = fmaf(-kzs[c], qsum, x0); x1 = fmaf(-kzs[c + 1], qsum, x1); }
+        const __half2 h2 = __floats2half2_rn(ex2(x0 - m_used), ex2(x1 - m_used));
+        const float2 pf = __half22float2(h2);               // the rounded values feed the normaliser too
+        if (VX) {
+            l_run = fmaf(pf.x, vinv[c], fmaf(pf.y, vinv[c + 1], l_run));
+            if (VZ) corr = fmaf(pf.x, vz[c], fmaf(pf.y, vz[c + 1], corr));
+        } else {
+            l_run += pf.x + pf.y;
+        }
+        ph[c >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
     }
 }
 
@@ -260,32 +368,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         if (a.kp.zp && r < nq) {
             for (int d = 0; d < D; ++d) qsum += load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + d);
         }
-        float m_used = -FLT_MAX, l_run = 0.f;
+        const bool v_exact = a.vp.group == D;               // V scale constant along head_dim: folded into P
+        const bool v_zp = v_exact && a.vp.zp != nullptr;
+        const bool k_zp = a.kp.zp != nullptr;
+        float m_used = -FLT_MAX, l_run = 0.f, corr = 0.f;
         bool ok = true;
         for (int j = 0; j < T && ok; ++j) {
             const int buf = j & 1;
-            const int n_valid = min(N, a.Lk - j * N);
-            ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1, abort_flag, 10);          // per-key K parameters are visible
+            ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1, abort_flag, 10);          // per-key parameters are visible
             if (ok) ok = mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + buf * 2 * N;
-            const float* kz = ks + N;
-            float x[N];
+            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + buf * 6 * N;
+            const float* b1 = ks + N;
+            const float* b2 = ks + 2 * N;
+            const float* kzs = ks + 3 * N;
+            const float* vinv = ks + 4 * N;
+            const float* vz = ks + 5 * N;
+            const uint32_t s_addr = lane_base + P::COL_S + buf * N;
+            // ---- pass 1: row maximum of this tile
             float m_tile = -FLT_MAX;
-#pragma unroll
+#pragma unroll 1
             for (int c0 = 0; c0 < N; c0 += 32) {
                 uint32_t raw[32];
-                tmem_ld32(lane_base + P::COL_S + buf * N + c0, raw);
+                tmem_ld32(s_addr + c0, raw);
                 tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    float v = __uint_as_float(raw[c]) * ks[c0 + c] - kz[c0 + c] * qsum;
-                    v = (c0 + c < n_valid) ? v : -FLT_MAX;
-                    x[c0 + c] = v;
-                    m_tile = fmaxf(m_tile, v);
-                }
+                m_tile = k_zp ? softmax_max32<true>(raw, ks + c0, b1 + c0, kzs + c0, qsum, m_tile)
+                              : softmax_max32<false>(raw, ks + c0, b1 + c0, kzs + c0, qsum, m_tile);
             }
             // lazy rescale: keep the running reference max until it is exceeded by more than 8 (log2 units)
             float alpha = 1.f;
@@ -311,21 +421,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 tmem_wait_st();
             }
             l_run *= alpha;
+            corr *= alpha;
             if (j >= 2) {   // the P buffer is free once the MMA that read it has completed
                 ok = mbar_wait(&bar_pv[buf], ((j - 2) >> 1) & 1, abort_flag, 13);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            unsigned char* sp = smem + P::OFF_P + buf * P::P_BYTES;
-#pragma unroll
-            for (int c0 = 0; c0 < N; c0 += 8) {
-                __half ph[8];
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    ph[c] = __float2half_rn(ex2(x[c0 + c] - m_used));
-                    l_run += __half2float(ph[c]);
+            // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
+            unsigned char* prow = smem + P::OFF_P + buf * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll 1
+            for (int c0 = 0; c0 < N; c0 += 32) {
+                uint32_t raw[32];
+                tmem_ld32(s_addr + c0, raw);
+                tmem_wait_ld();
+                uint32_t ph[16];
+                if (!v_exact) {
+                    if (k_zp) softmax_exp32<true, false, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    else      softmax_exp32<false, false, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                } else if (v_zp) {
+                    if (k_zp) softmax_exp32<true, true, true>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    else      softmax_exp32<false, true, true>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                } else {
+                    if (k_zp) softmax_exp32<true, true, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    else      softmax_exp32<false, true, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
                 }
-                *reinterpret_cast<uint4*>(sp + tile_off(r, c0, TC_M)) = *reinterpret_cast<uint4*>(ph);
+                unsigned char* blk = prow + (c0 >> 6) * (TC_M * 128);
+                const int ch0 = (c0 & 63) >> 3;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    *reinterpret_cast<uint4*>(blk + (((ch0 + q4) ^ (r & 7)) << 4)) = make_uint4(ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
             }
             fence_async_smem();
             tc_fence_before();
@@ -345,7 +469,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     const long long off = b * a.os_b + (long long)(q0 + r) * a.os_l + h * a.os_h + c0;
                     float v[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(raw[c]) * inv;
+                    for (int c = 0; c < 32; ++c) v[c] = (__uint_as_float(raw[c]) - corr) * inv;
                     store_o_row32(a.out, a.o_dtype, off, v);
                 }
             }
@@ -385,22 +509,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             unsigned char* tk = smem + P::OFF_K + s * P::KV_BYTES;
             unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
-            if (kb == 8) dequant_tile<8, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
-            else if (kb == 4) dequant_tile<4, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
-            else dequant_tile<2, true>(tk, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
-            if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-            else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-            else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-            if (ptid < N) {   // per-key K parameters, pre-multiplied by softmax_scale * log2(e)
-                float* ks = reinterpret_cast<float*>(smem + P::OFF_KS) + s * 2 * N;
-                float sc = 0.f, zs = 0.f;
+            if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
+            else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
+            else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
+            const bool v_exact = a.vp.group == D;
+            if (v_exact) {
+                if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid);
+                else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid);
+                else codes_tile<2>(tv, pv, n_valid, N, wv, ptid);
+            } else {
+                if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+                else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+                else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+            }
+            if (ptid < N) {   // per-key parameters; the K scale carries softmax_scale * log2(e)
+                float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + s * 6 * N;
+                float sc = 0.f, zs = 0.f, vsc = 1.f, vzp = 0.f, bias = -1e30f;
                 if (ptid < n_valid) {
                     const long long pi = a.kp.index(b, a.kp.row(k0 + ptid), h, 0);
                     sc = __ldg(a.kp.scale + pi) * a.scale_log2;
                     zs = a.kp.zp ? __ldg(a.kp.zp + pi) * sc : 0.f;
+                    bias = 0.f;
+                    if (v_exact) {
+                        const long long vi = a.vp.index(b, a.vp.row(k0 + ptid), h, 0);
+                        vsc = __ldg(a.vp.scale + vi);
+                        vzp = a.vp.zp ? __ldg(a.vp.zp + vi) : 0.f;
+                    }
                 }
-                ks[ptid] = sc;
-                ks[N + ptid] = zs;
+                tab[ptid] = sc;
+                tab[N + ptid] = bias;
+                tab[2 * N + ptid] = bias + __log2f(vsc);
+                tab[3 * N + ptid] = zs;
+                tab[4 * N + ptid] = __fdividef(1.f, vsc);
+                tab[5 * N + ptid] = vzp;
             }
             fence_async_smem();
             mbar_arrive(&bar_kv[s]);
