@@ -29,7 +29,8 @@ def run(path, q, kq, vq, scale, out_dtype=torch.float32):
     n0 = _cabi.lib().varq_launch_count()
     out = attend_cached(q, kq, vq, scale, out_dtype=out_dtype)
     torch.cuda.synchronize()
-    assert _cabi.device_status() == 0, "a kernel wait expired"
+    status = _cabi.device_status()
+    assert status == 0, f"a kernel wait expired (code {status})"
     return out, _cabi.lib().varq_launch_count() - n0
 
 

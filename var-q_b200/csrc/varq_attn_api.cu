@@ -51,7 +51,7 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     a.k16 = words_aligned16(k_codes, wk);
     a.v16 = words_aligned16(v_codes, wv);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
-    a.splits = 1; a.tiles_per_split = 0; a.ws = nullptr;
+    a.splits = 1; a.tiles_per_split = 0; a.ws = reinterpret_cast<float*>(workspace);
     // small query counts stay on the CUDA-core kernel (memory-bound); the rest goes to the tensor cores
     const char* force = getenv("VARQ_ATTN_PATH");       // "small" / "tc": testing aid, not a fallback switch
     const bool want_tc = force ? (force[0] == 't') : (Lq > 8);

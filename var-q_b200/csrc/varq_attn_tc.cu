@@ -1,13 +1,14 @@
 // Attention over the packed cache on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Nine warps:
-//   warps 0-3  softmax: thread r owns query row r (TMEM lane r); reads S from TMEM, applies the
-//              per-key scale / zero-point of K, online softmax with lazy rescaling of O, writes
-//              P (fp16) to shared memory, final normalisation and store;
-//   warps 4-7  producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
+// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Thirteen warps:
+//   warps 0-7  softmax: two threads share query row r (TMEM lane r), each taking half of the
+//              tile's keys; they read S from TMEM, apply the per-key scale / zero-point of K,
+//              do the online softmax with lazy rescaling of O, write P (fp16) to shared memory,
+//              and at the end normalise and store;
+//   warps 8-11 producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
 //              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
 //              K as exact fp16 integer codes, V as fp16 (code - zp) * scale;
-//   warp  8    one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
+//   warp  12   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
 //              O += P V, and commits completion to mbarriers.
 // Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
 // no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
@@ -19,9 +20,20 @@
 
 namespace varq {
 
-constexpr int TC_THREADS = 288;
+constexpr int TC_THREADS = 416;   // 8 softmax warps, 4 producer warps, 1 MMA warp
 constexpr int TC_M = 128;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
+
+#ifdef VARQ_TC_TRACE
+// development aid: cycle stamps of CTA (0,0), [role][tile][event], written to the workspace pointer
+#define TC_TRACE(role, j, ev)                                                                      \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && a.ws && (j) < 32)      \
+            reinterpret_cast<long long*>(a.ws)[((role) * 32 + (j)) * 8 + (ev)] = clock64();        \
+    } while (0)
+#else
+#define TC_TRACE(role, j, ev) do { } while (0)
+#endif
 
 __device__ int g_tc_status = 0;   // first failure code of any launch since the last read (0 = none)
 
@@ -134,11 +146,12 @@ template <int D, int NQ> struct TcPlan {
     static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;        // [2]
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [2]
     static constexpr int OFF_PK = OFF_P + 2 * P_BYTES;        // [2][K, V]
-    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [2][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
-    static constexpr int OFF_BAR = OFF_KS + 2 * 6 * N * 4;    // mbarriers
-    static constexpr int N_BARS = 11;
+    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
+    static constexpr int OFF_BAR = OFF_KS + 4 * 6 * N * 4;    // mbarriers
+    static constexpr int N_BARS = 17;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
-    static constexpr int TOTAL = OFF_MISC + 16;
+    static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][2][2][128]: row halves exchange (parity, slot, half, row)
+    static constexpr int TOTAL = OFF_XCH + 2 * 2 * 2 * 128 * 4;
     static constexpr int TMEM_COLS = (2 * N + D) <= 256 ? 256 : 512;
     static constexpr int COL_S = 0, COL_O = 2 * N;
 };
@@ -262,14 +275,24 @@ __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t
 // ---- softmax over 32 columns of S held in registers.  Per-key tables (shared memory):
 // ks = K scale * softmax_scale * log2(e) (0 past the end), b1 = 0 / -1e30 mask bias,
 // b2 = b1 + log2(V scale), kzs = K zero-point * ks, vinv = 1 / V scale, vz = V zero-point.
+// four consecutive table entries with one 16-byte shared-memory load (tables are 16-byte aligned)
+__device__ __forceinline__ float4 tab4(const float* p, int c) { return *reinterpret_cast<const float4*>(p + c); }
+__device__ __forceinline__ float pick(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
 template <bool KZ>
 __device__ __forceinline__ float softmax_max32(const uint32_t (&raw)[32], const float* ks, const float* b1,
                                                const float* kzs, float qsum, float m) {
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-        float v = fmaf(__uint_as_float(raw[c]), ks[c], b1[c]);
-        if (KZ) v = fmaf(-kzs[c], qsum, v);
-        m = fmaxf(m, v);
+    for (int c = 0; c < 32; c += 4) {
+        const float4 s4 = tab4(ks, c), b4 = tab4(b1, c);
+        float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (KZ) z4 = tab4(kzs, c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float v = fmaf(__uint_as_float(raw[c + i]), pick(s4, i), pick(b4, i));
+            if (KZ) v = fmaf(-pick(z4, i), qsum, v);
+            m = fmaxf(m, v);
+        }
     }
     return m;
 }
@@ -277,21 +300,34 @@ template <bool KZ, bool VX, bool VZ>
 __device__ __forceinline__ void softmax_exp32(const uint32_t (&raw)[32], uint32_t (&ph)[16], const float* ks,
                                               const float* b2, const float* kzs, const float* vinv, const float* vz,
                                               float qsum, float m_used, float& l_run, float& corr) {
+    float l0 = 0.f, l1 = 0.f, c0s = 0.f, c1s = 0.f;        // two accumulators shorten the dependent chains
 #pragma unroll
-    for (int c = 0; c < 32; c += 2) {
-        float x0 = fmaf(__uint_as_float(raw[c]), ks[c], b2[c]);
-        float x1 = fmaf(__uint_as_float(raw[c + 1]), ks[c + 1], b2[c + 1]);
-        if (KZ) { x0 = fmaf(-kzs[c], qsum, x0); x1 = fmaf(-kzs[c + 1], qsum, x1); }
-        const __half2 h2 = __floats2half2_rn(ex2(x0 - m_used), ex2(x1 - m_used));
-        const float2 pf = __half22float2(h2);               // the rounded values feed the normaliser too
-        if (VX) {
-            l_run = fmaf(pf.x, vinv[c], fmaf(pf.y, vinv[c + 1], l_run));
-            if (VZ) corr = fmaf(pf.x, vz[c], fmaf(pf.y, vz[c + 1], corr));
-        } else {
-            l_run += pf.x + pf.y;
+    for (int c = 0; c < 32; c += 4) {
+        const float4 s4 = tab4(ks, c), b4 = tab4(b2, c);
+        float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f), i4 = z4, w4 = z4;
+        if (KZ) z4 = tab4(kzs, c);
+        if (VX) i4 = tab4(vinv, c);
+        if (VZ) w4 = tab4(vz, c);
+#pragma unroll
+        for (int i = 0; i < 4; i += 2) {
+            float x0 = fmaf(__uint_as_float(raw[c + i]), pick(s4, i), pick(b4, i));
+            float x1 = fmaf(__uint_as_float(raw[c + i + 1]), pick(s4, i + 1), pick(b4, i + 1));
+            if (KZ) { x0 = fmaf(-pick(z4, i), qsum, x0); x1 = fmaf(-pick(z4, i + 1), qsum, x1); }
+            const __half2 h2 = __floats2half2_rn(ex2(x0 - m_used), ex2(x1 - m_used));
+            const float2 pf = __half22float2(h2);           // the rounded values feed the normaliser too
+            if (VX) {
+                l0 = fmaf(pf.x, pick(i4, i), l0);
+                l1 = fmaf(pf.y, pick(i4, i + 1), l1);
+                if (VZ) { c0s = fmaf(pf.x, pick(w4, i), c0s); c1s = fmaf(pf.y, pick(w4, i + 1), c1s); }
+            } else {
+                l0 += pf.x;
+                l1 += pf.y;
+            }
+            ph[(c + i) >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
         }
-        ph[c >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
     }
+    l_run += l0 + l1;
+    corr += c0s + c1s;
 }
 
 template <int D, int NQ>
@@ -302,11 +338,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
     uint64_t* bar_pk = bars;          // [2] packed K+V rows landed (tx bytes)
-    uint64_t* bar_kv = bars + 2;      // [2] fp16 K/V operand tiles written (128 producers)
-    uint64_t* bar_s = bars + 4;       // [2] S = Q K^T complete (tcgen05.commit)
-    uint64_t* bar_p = bars + 6;       // [2] P written, O rescaled (128 softmax threads)
-    uint64_t* bar_pv = bars + 8;      // [2] O += P V complete (tcgen05.commit)
-    uint64_t* bar_o = bars + 10;      // all MMAs complete
+    uint64_t* bar_k = bars + 2;       // [2] K operand tile and per-key tables written (128 producers)
+    uint64_t* bar_v = bars + 4;       // [2] V operand tile written (128 producers)
+    uint64_t* bar_s = bars + 6;       // [2] S = Q K^T complete (tcgen05.commit): K stage free again
+    uint64_t* bar_p = bars + 8;       // [2] P written, O rescaled (256 softmax threads)
+    uint64_t* bar_pv = bars + 10;     // [2] O += P V complete (tcgen05.commit): V stage and P buffer free
+    uint64_t* bar_o = bars + 12;      // all MMAs complete
+    uint64_t* bar_t = bars + 13;      // [4] per-key tables of tile j written (slot j % 4; 128 producers)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
 
@@ -320,16 +358,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_pk[i], 1);
-            mbar_init(&bar_kv[i], 128);
+            mbar_init(&bar_k[i], 128);
+            mbar_init(&bar_v[i], 128);
             mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_p[i], 128);
+            mbar_init(&bar_p[i], 256);
             mbar_init(&bar_pv[i], 1);
         }
         mbar_init(bar_o, 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&bar_t[i], 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {   // TMEM allocation by one full warp
+    if (warp == 12) {   // TMEM allocation by one full warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -360,43 +400,66 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
     const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
 
-    if (warp < 4) {
+    if (warp < 8) {
         // =============================================================== softmax / epilogue
-        const int r = tid;                                  // query row = TMEM lane
-        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float qsum = 0.f;
-        if (a.kp.zp && r < nq) {
-            for (int d = 0; d < D; ++d) qsum += load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + d);
-        }
+        constexpr int NH = N / 2;                           // keys per thread and tile
+        constexpr int DH = D / 2;                           // output columns per thread
+        const int quarter = warp & 3, half = warp >> 2;
+        const int r = quarter * 32 + lane;                  // query row = TMEM lane
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float* xch = reinterpret_cast<float*>(smem + P::OFF_XCH);
+        // the two warps that share a TMEM lane quarter agree on `ok` and meet at a named barrier
+        auto pair_sync_and = [&](bool flag) -> bool {
+            uint32_t all_ok;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 64, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(all_ok) : "r"((uint32_t)flag), "r"(3 + quarter) : "memory");
+            return all_ok != 0;
+        };
         const bool v_exact = a.vp.group == D;               // V scale constant along head_dim: folded into P
         const bool v_zp = v_exact && a.vp.zp != nullptr;
         const bool k_zp = a.kp.zp != nullptr;
+        float qsum = 0.f;
+        if (k_zp && r < nq) {
+            for (int d = 0; d < D; ++d) qsum += load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + d);
+        }
         float m_used = -FLT_MAX, l_run = 0.f, corr = 0.f;
         bool ok = true;
-        for (int j = 0; j < T && ok; ++j) {
+        for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
-            ok = mbar_wait(&bar_kv[buf], (j >> 1) & 1, abort_flag, 10);          // per-key parameters are visible
-            if (ok) ok = mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
+            ok = ok && mbar_wait(&bar_t[j & 3], (j >> 2) & 1, abort_flag, 10);   // per-key tables are visible
+            ok = ok && mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + buf * 6 * N;
+            if (quarter == 0) TC_TRACE(half, j, 0);
+            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & 3) * 6 * N + half * NH;
             const float* b1 = ks + N;
             const float* b2 = ks + 2 * N;
             const float* kzs = ks + 3 * N;
             const float* vinv = ks + 4 * N;
             const float* vz = ks + 5 * N;
-            const uint32_t s_addr = lane_base + P::COL_S + buf * N;
-            // ---- pass 1: row maximum of this tile
-            float m_tile = -FLT_MAX;
-#pragma unroll 1
-            for (int c0 = 0; c0 < N; c0 += 32) {
-                uint32_t raw[32];
-                tmem_ld32(s_addr + c0, raw);
+            const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
+            // ---- this thread's half row of S, read from TMEM once; pass 1: its maximum
+            uint32_t raw[NH];
+            float m_half = -FLT_MAX;
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < NH; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(raw + c0));
                 tmem_wait_ld();
-                m_tile = k_zp ? softmax_max32<true>(raw, ks + c0, b1 + c0, kzs + c0, qsum, m_tile)
-                              : softmax_max32<false>(raw, ks + c0, b1 + c0, kzs + c0, qsum, m_tile);
+                if (quarter == 0) TC_TRACE(half, j, 5);
+#pragma unroll
+                for (int c0 = 0; c0 < NH; c0 += 32) {
+                    const uint32_t(&rw)[32] = *reinterpret_cast<const uint32_t(*)[32]>(raw + c0);
+                    m_half = k_zp ? softmax_max32<true>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half)
+                                  : softmax_max32<false>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half);
+                }
             }
+            if (quarter == 0) TC_TRACE(half, j, 1);
+            float* slot = xch + (j & 1) * 512;              // [slot 0][half][row]
+            slot[half * 128 + r] = m_half;
+            ok = pair_sync_and(ok);
+            if (!ok) break;
+            if (quarter == 0) TC_TRACE(half, j, 2);
+            const float m_tile = fmaxf(m_half, slot[(half ^ 1) * 128 + r]);
             // lazy rescale: keep the running reference max until it is exceeded by more than 8 (log2 units)
             float alpha = 1.f;
             const bool need = m_tile > m_used + 8.f || j == 0;
@@ -407,77 +470,86 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (__any_sync(0xffffffffu, need) && j > 0) {
                 ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 12);   // O is stable
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
+                if (ok) {
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < DH; c0 += 32) {
+                        uint32_t raw[32];
+                        tmem_ld32(lane_base + P::COL_O + half * DH + c0, raw);
+                        tmem_wait_ld();
 #pragma unroll
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t raw[32];
-                    tmem_ld32(lane_base + P::COL_O + c0, raw);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-                    tmem_st32(lane_base + P::COL_O + c0, raw);
+                        for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
+                        tmem_st32(lane_base + P::COL_O + half * DH + c0, raw);
+                    }
+                    tmem_wait_st();
                 }
-                tmem_wait_st();
             }
             l_run *= alpha;
             corr *= alpha;
-            if (j >= 2) {   // the P buffer is free once the MMA that read it has completed
+            if (ok && j >= 2) {   // the P buffer is free once the MMA that read it has completed
                 ok = mbar_wait(&bar_pv[buf], ((j - 2) >> 1) & 1, abort_flag, 13);
                 ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
             }
-            // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
-            unsigned char* prow = smem + P::OFF_P + buf * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll 1
-            for (int c0 = 0; c0 < N; c0 += 32) {
-                uint32_t raw[32];
-                tmem_ld32(s_addr + c0, raw);
-                tmem_wait_ld();
-                uint32_t ph[16];
-                if (!v_exact) {
-                    if (k_zp) softmax_exp32<true, false, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                    else      softmax_exp32<false, false, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                } else if (v_zp) {
-                    if (k_zp) softmax_exp32<true, true, true>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                    else      softmax_exp32<false, true, true>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                } else {
-                    if (k_zp) softmax_exp32<true, true, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                    else      softmax_exp32<false, true, false>(raw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                }
-                unsigned char* blk = prow + (c0 >> 6) * (TC_M * 128);
-                const int ch0 = (c0 & 63) >> 3;
+            if (quarter == 0) TC_TRACE(half, j, 3);
+            if (ok) {
+                // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
+                unsigned char* prow = smem + P::OFF_P + buf * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    *reinterpret_cast<uint4*>(blk + (((ch0 + q4) ^ (r & 7)) << 4)) = make_uint4(ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
+                for (int c0 = 0; c0 < NH; c0 += 32) {
+                    const uint32_t(&rw)[32] = *reinterpret_cast<const uint32_t(*)[32]>(raw + c0);
+                    uint32_t ph[16];
+                    if (!v_exact) {
+                        if (k_zp) softmax_exp32<true, false, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                        else      softmax_exp32<false, false, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    } else if (v_zp) {
+                        if (k_zp) softmax_exp32<true, true, true>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                        else      softmax_exp32<false, true, true>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    } else {
+                        if (k_zp) softmax_exp32<true, true, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                        else      softmax_exp32<false, true, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    }
+                    const int col = half * NH + c0;         // key index of the chunk inside the tile
+                    unsigned char* blk = prow + (col >> 6) * (TC_M * 128);
+                    const int ch0 = (col & 63) >> 3;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<uint4*>(blk + (((ch0 + q4) ^ (r & 7)) << 4)) = make_uint4(ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
+                }
+                fence_async_smem();
+                tc_fence_before();
+                mbar_arrive(&bar_p[buf]);
+                if (quarter == 0) TC_TRACE(half, j, 4);
             }
-            fence_async_smem();
-            tc_fence_before();
-            mbar_arrive(&bar_p[buf]);
         }
-        if (ok) ok = mbar_wait(bar_o, 0, abort_flag, 14);
+        // ---- the two halves of a row add up their normalisers, then each stores half of the columns
+        float* fin = xch + 256;                             // [parity][slot 1][half][row]: free of max traffic
+        fin[half * 128 + r] = l_run;
+        fin[512 + half * 128 + r] = corr;
+        ok = ok && mbar_wait(bar_o, 0, abort_flag, 14);
         ok = __all_sync(0xffffffffu, ok);
+        ok = pair_sync_and(ok);
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / l_run;
-#pragma unroll
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            const float inv = 1.f / (l_run + fin[(half ^ 1) * 128 + r]);
+            const float corr_row = corr + fin[512 + (half ^ 1) * 128 + r];
+#pragma unroll 1
+            for (int c0 = 0; c0 < DH; c0 += 32) {
                 uint32_t raw[32];
-                tmem_ld32(lane_base + P::COL_O + c0, raw);
+                tmem_ld32(lane_base + P::COL_O + half * DH + c0, raw);
                 tmem_wait_ld();
                 if (r < nq) {
-                    const long long off = b * a.os_b + (long long)(q0 + r) * a.os_l + h * a.os_h + c0;
+                    const long long off = b * a.os_b + (long long)(q0 + r) * a.os_l + h * a.os_h + half * DH + c0;
                     float v[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = (__uint_as_float(raw[c]) - corr) * inv;
+                    for (int c = 0; c < 32; ++c) v[c] = (__uint_as_float(raw[c]) - corr_row) * inv;
                     store_o_row32(a.out, a.o_dtype, off, v);
                 }
             }
         }
         tc_fence_before();
-    } else if (warp < 8) {
+    } else if (warp < 12) {
         // =============================================================== producers
-        const int ptid = tid - 128;
+        const int ptid = tid - 256;
         auto issue = [&](int j) {
             const int s = j & 1;
             const int n_valid = min(N, a.Lk - j * N);
@@ -492,60 +564,83 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         bool ok = true;
         int issued = min(T, 2);
+        const bool v_exact = a.vp.group == D;
+        // per-key parameters of a tile are fetched one tile ahead so the global-load latency is hidden
+        float nsc = 0.f, nzs = 0.f, nvsc = 1.f, nvzp = 0.f;
+        auto fetch_params = [&](int j) {
+            nsc = 0.f; nzs = 0.f; nvsc = 1.f; nvzp = 0.f;
+            const int key = j * N + ptid;
+            if (j < T && ptid < N && key < a.Lk) {
+                const long long pi = a.kp.index(b, a.kp.row(key), h, 0);
+                nsc = __ldg(a.kp.scale + pi);
+                if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
+                if (v_exact) {
+                    const long long vi = a.vp.index(b, a.vp.row(key), h, 0);
+                    nvsc = __ldg(a.vp.scale + vi);
+                    if (a.vp.zp) nvzp = __ldg(a.vp.zp + vi);
+                }
+            }
+        };
+        fetch_params(0);
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
             const int k0 = j * N;
             const int n_valid = min(N, a.Lk - k0);
-            ok = mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
-            if (ok && j >= 2) ok = mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 22);   // operand stage is free
-            {   // all 128 producers take the same decision, so none is left alone at the barrier below
-                uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
-                ok = all_ok != 0;
-            }
-            if (!ok) break;
+            if (warp == 8) TC_TRACE(2, j, 0);
+            const float sc = nsc, zs = nzs, vsc = nvsc, vzp = nvzp;
+            const float bias = (ptid < n_valid) ? 0.f : -1e30f;
+            fetch_params(j + 1);
+            ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
+            if (warp == 8) TC_TRACE(2, j, 1);
+            if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
+            if (warp == 8) TC_TRACE(2, j, 2);
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             unsigned char* tk = smem + P::OFF_K + s * P::KV_BYTES;
             unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
-            if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
-            else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
-            else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
-            const bool v_exact = a.vp.group == D;
-            if (v_exact) {
-                if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid);
-                else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid);
-                else codes_tile<2>(tv, pv, n_valid, N, wv, ptid);
-            } else {
-                if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-                else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-                else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-            }
-            if (ptid < N) {   // per-key parameters; the K scale carries softmax_scale * log2(e)
-                float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + s * 6 * N;
-                float sc = 0.f, zs = 0.f, vsc = 1.f, vzp = 0.f, bias = -1e30f;
-                if (ptid < n_valid) {
-                    const long long pi = a.kp.index(b, a.kp.row(k0 + ptid), h, 0);
-                    sc = __ldg(a.kp.scale + pi) * a.scale_log2;
-                    zs = a.kp.zp ? __ldg(a.kp.zp + pi) * sc : 0.f;
-                    bias = 0.f;
-                    if (v_exact) {
-                        const long long vi = a.vp.index(b, a.vp.row(k0 + ptid), h, 0);
-                        vsc = __ldg(a.vp.scale + vi);
-                        vzp = a.vp.zp ? __ldg(a.vp.zp + vi) : 0.f;
-                    }
+            if (ok) {
+                if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
+                else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
+                else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
+                if (warp == 8) TC_TRACE(2, j, 6);
+                if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
+                    float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 6 * N;
+                    const float scl = sc * a.scale_log2;
+                    tab[ptid] = scl;
+                    tab[N + ptid] = bias;
+                    tab[2 * N + ptid] = bias + __log2f(vsc);
+                    tab[3 * N + ptid] = zs * scl;
+                    tab[4 * N + ptid] = __fdividef(1.f, vsc);
+                    tab[5 * N + ptid] = vzp;
                 }
-                tab[ptid] = sc;
-                tab[N + ptid] = bias;
-                tab[2 * N + ptid] = bias + __log2f(vsc);
-                tab[3 * N + ptid] = zs;
-                tab[4 * N + ptid] = __fdividef(1.f, vsc);
-                tab[5 * N + ptid] = vzp;
+                fence_async_smem();
+                mbar_arrive(&bar_k[s]);
+                mbar_arrive(&bar_t[j & 3]);
             }
-            fence_async_smem();
-            mbar_arrive(&bar_kv[s]);
-            asm volatile("bar.sync 1, 128;" ::: "memory");      // every producer is done with the packed stage
+            if (warp == 8) TC_TRACE(2, j, 3);
+            if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
+            if (warp == 8) TC_TRACE(2, j, 4);
+            if (ok) {
+                if (v_exact) {
+                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid);
+                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid);
+                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid);
+                } else {
+                    if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+                    else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+                    else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
+                }
+                fence_async_smem();
+                mbar_arrive(&bar_v[s]);
+            }
+            if (warp == 8) TC_TRACE(2, j, 5);
+            {   // every producer is done with the packed stage; all 128 take the same decision on `ok`
+                uint32_t all_ok;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+                ok = all_ok != 0;
+            }
+            if (!ok) break;
             if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
         }
         if (!ok && ptid == 0) {
@@ -561,43 +656,51 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         constexpr uint32_t IDESC_O = instr_desc(TC_M, D, 1);
         const uint32_t q_addr = smem_u32(smem + P::OFF_Q);
         bool ok = true;
+        // descriptors differ from their stage base only in the start-address field (bits 0-13, 16-byte units)
+        const uint64_t qd0 = smem_desc(q_addr, 16, 1024);
+        const uint64_t kd0 = smem_desc(smem_u32(smem + P::OFF_K), 16, 1024);
+        const uint64_t pd0 = smem_desc(smem_u32(smem + P::OFF_P), 16, 1024);
+        const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), N * 128, 1024);
         auto issue_pv = [&](int j) {
             const int s = j & 1;
-            const uint32_t p_addr = smem_u32(smem + P::OFF_P + s * P::P_BYTES);
-            const uint32_t v_addr = smem_u32(smem + P::OFF_V + s * P::KV_BYTES);
+            const uint64_t pd = pd0 + (uint64_t)((s * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < N / 16; ++kk) {
-                const uint64_t ad = smem_desc(p_addr + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32, 16, 1024);
-                const uint64_t bd = smem_desc(v_addr + kk * 2048, N * 128, 1024);
-                tc_mma_f16(tmem_base + P::COL_O, ad, bd, IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
-            }
+            for (int kk = 0; kk < N / 16; ++kk)
+                tc_mma_f16(tmem_base + P::COL_O, pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                           vd + (uint64_t)((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bar_pv[s]);
         };
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
-            ok = mbar_wait(&bar_kv[s], (j >> 1) & 1, abort_flag, 31);
+            TC_TRACE(3, j, 0);
+            ok = mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31);
             if (!ok) break;
+            TC_TRACE(3, j, 1);
             tc_fence_after();
-            const uint32_t k_addr = smem_u32(smem + P::OFF_K + s * P::KV_BYTES);
+            const uint64_t kd = kd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
 #pragma unroll
             for (int qi = 0; qi < NQ; ++qi) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t ad = smem_desc(q_addr + qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = smem_desc(k_addr + (kk >> 2) * (N * 128) + (kk & 3) * 32, 16, 1024);
-                    tc_mma_f16(tmem_base + P::COL_S + s * N, ad, bd, IDESC_S, (qi > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < D / 16; ++kk)
+                    tc_mma_f16(tmem_base + P::COL_S + s * N,
+                               qd0 + (uint64_t)((qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                               kd + (uint64_t)(((kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S, (qi > 0 || kk > 0) ? 1u : 0u);
             }
             tc_commit(&bar_s[s]);
+            TC_TRACE(3, j, 2);
             if (j >= 1) {
-                ok = mbar_wait(&bar_p[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 32);
+                const int sp = (j - 1) & 1;
+                ok = mbar_wait(&bar_p[sp], ((j - 1) >> 1) & 1, abort_flag, 32) &&
+                     mbar_wait(&bar_v[sp], ((j - 1) >> 1) & 1, abort_flag, 34);
                 if (!ok) break;
+                TC_TRACE(3, j, 3);
                 tc_fence_after();
                 issue_pv(j - 1);
             }
         }
         if (ok) {
-            ok = mbar_wait(&bar_p[(T - 1) & 1], ((T - 1) >> 1) & 1, abort_flag, 33);
+            const int sp = (T - 1) & 1;
+            ok = mbar_wait(&bar_p[sp], ((T - 1) >> 1) & 1, abort_flag, 33) && mbar_wait(&bar_v[sp], ((T - 1) >> 1) & 1, abort_flag, 35);
             if (ok) {
                 tc_fence_after();
                 issue_pv(T - 1);
@@ -607,7 +710,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 12) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
     }
