@@ -74,6 +74,7 @@ struct RowPlan {
     int lpg;        // lanes per group = group / VPW
     long long n_gr; // group rows in total: L*H (shared batch) or B*L*H
     int h_fast;     // group-row enumeration: 1 = head index fastest
+    int d_in, d_mid, d_out;   // ngr decomposed in the (inner, middle, batch) radices of that enumeration
 };
 
 template <typename T, int STORE_BITS>
@@ -100,21 +101,42 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
     long long xoff[NVMAX];                   // element offset of the vector, -1 = not present
     int vb[NVMAX], vl[NVMAX], vh[NVMAX];
 
+    // (b, l, h) of the thread's first vector; the others follow by constant steps (no per-vector division)
+    const unsigned n_gr = (unsigned)pl.n_gr;                 // host guarantees < 2^31
+    unsigned gr0 = a.share_b ? blockIdx.x * (unsigned)pl.ngr + g_local
+                             : blockIdx.x * (unsigned)(pl.nv * pl.ngr) + g_local;
+    int b0, l0, h0;
+    {
+        unsigned g = gr0;
+        if (pl.h_fast) { h0 = (int)(g % (unsigned)a.H); g /= (unsigned)a.H; l0 = (int)(g % (unsigned)a.L); g /= (unsigned)a.L; }
+        else           { l0 = (int)(g % (unsigned)a.L); g /= (unsigned)a.L; h0 = (int)(g % (unsigned)a.H); g /= (unsigned)a.H; }
+        b0 = a.share_b ? bl : (int)g;
+    }
+    int cb = b0, cl = l0, ch = h0;           // running coordinates when the batch is not shared
 #pragma unroll
     for (int k = 0; k < NVMAX; ++k) {
         xoff[k] = -1;
         if (k < pl.nv) {
-            long long gr;
-            int b;
-            if (a.share_b) { gr = (long long)blockIdx.x * pl.ngr + g_local; b = bl + k * pl.bp; }
-            else           { gr = ((long long)blockIdx.x * pl.nv + k) * pl.ngr + g_local; b = 0; }
-            if (gr < pl.n_gr && b < a.B) {
-                int l, h;
-                if (pl.h_fast) { h = (int)(gr % a.H); gr /= a.H; l = (int)(gr % a.L); gr /= a.L; }
-                else           { l = (int)(gr % a.L); gr /= a.L; h = (int)(gr % a.H); gr /= a.H; }
-                if (!a.share_b) b = (int)gr;
-                vb[k] = b; vl[k] = l; vh[k] = h;
-                xoff[k] = b * a.xs_b + l * a.xs_l + h * a.xs_h + d0;
+            bool ok_k;
+            if (a.share_b) {
+                cb = bl + k * pl.bp;
+                ok_k = gr0 < n_gr && cb < a.B;
+            } else {
+                if (k > 0) {   // advance the mixed-radix counter by ngr group rows (steps precomputed on the host)
+                    if (pl.h_fast) {
+                        ch += pl.d_in;  if (ch >= a.H) { ch -= a.H; ++cl; }
+                        cl += pl.d_mid; if (cl >= a.L) { cl -= a.L; ++cb; }
+                    } else {
+                        cl += pl.d_in;  if (cl >= a.L) { cl -= a.L; ++ch; }
+                        ch += pl.d_mid; if (ch >= a.H) { ch -= a.H; ++cb; }
+                    }
+                    cb += pl.d_out;
+                }
+                ok_k = gr0 + (unsigned)k * (unsigned)pl.ngr < n_gr;
+            }
+            if (ok_k) {
+                vb[k] = cb; vl[k] = cl; vh[k] = ch;
+                xoff[k] = cb * a.xs_b + cl * a.xs_l + ch * a.xs_h + d0;
             }
         }
     }
@@ -203,9 +225,12 @@ __device__ __forceinline__ void stats_flush(uint32_t* stats, long long gid, cons
     if (!sym) atomicMax(&stats[gid * 2 + 1], r.lo);
 }
 
+constexpr int TAB_UNROLL = 4;   // independent row loads in flight per thread
+
 template <typename T, int STORE_BITS, bool VEC>
-__global__ void quant_stats_kernel(QuantArgs a, int iters) {
+__global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
+    extern __shared__ uint32_t s_fold[];            // [blockDim.x * VPW][2] when rows are folded in the block
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     const bool col_ok = cs < a.H * a.words;
     const int h = col_ok ? cs / a.words : 0, w = col_ok ? cs % a.words : 0;
@@ -214,66 +239,61 @@ __global__ void quant_stats_kernel(QuantArgs a, int iters) {
     const bool sym = a.symmetric != 0;
     const bool uniform = (a.group % VPW) == 0;      // one group per thread-vector
     const bool row_dep = !(a.share_b && a.share_l); // group depends on the (b, l) row
-    const long long R = (long long)a.B * a.L;
-    const long long r_step = (long long)gridDim.y * blockDim.y;
+    const unsigned R = (unsigned)a.B * (unsigned)a.L;       // host guarantees < 2^31
+    const unsigned r_step = gridDim.y * blockDim.y;
+    const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
     Range acc[VPW];
 #pragma unroll
     for (int j = 0; j < VPW; ++j) range_init(acc[j]);
 
-    long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
-    for (int it = 0; it < iters; ++it, r += r_step) {
-        const bool ok = col_ok && r < R;
-        int b = 0, l = 0;
-        if (ok) {
-            b = (int)(r / a.L); l = (int)(r % a.L);
-            float v[VPW];
-            load_vals<T, VPW, VEC>(reinterpret_cast<const T*>(a.x) + b * a.xs_b + l * a.xs_l + h * a.xs_h + d0, v, n_valid);
-            if (uniform) {
-#pragma unroll
-                for (int j = 0; j < VPW; ++j) if (j < n_valid) range_add(acc[0], v[j], sym);
-            } else {
-#pragma unroll
-                for (int j = 0; j < VPW; ++j) if (j < n_valid) range_add(acc[j], v[j], sym);
-            }
-        }
-        if (row_dep) {
-            if (uniform) {
-                // the whole warp often sits in one group (per-token statistics): fold it first
-                const long long gid = ok ? group_id(a, b, l, h, d0) : -1;
-                int same;
-                __match_all_sync(0xffffffffu, gid, &same);
-                if (same) {
-                    if (gid >= 0) {
-                        Range t;
-                        t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
-                        t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
-                        if ((threadIdx.y * blockDim.x + threadIdx.x) % 32 == 0) stats_flush(a.stats, gid, t, sym);
-                    }
-                } else if (ok) {
-                    stats_flush(a.stats, gid, acc[0], sym);
-                }
-                range_init(acc[0]);
-            } else if (ok) {
-#pragma unroll
-                for (int j = 0; j < VPW; ++j) {
-                    if (j < n_valid) stats_flush(a.stats, group_id(a, b, l, h, d0 + j), acc[j], sym);
-                    range_init(acc[j]);
-                }
-            }
-        }
-    }
+    unsigned r = blockIdx.y * blockDim.y + threadIdx.y;
     if (!row_dep) {
+        // ---- statistics do not depend on the row: accumulate in registers, several loads in flight
+        for (int it = 0; it < iters; it += TAB_UNROLL) {
+            float v[TAB_UNROLL][VPW];
+            bool ok[TAB_UNROLL];
+#pragma unroll
+            for (int u = 0; u < TAB_UNROLL; ++u) {
+                const unsigned ru = r + u * r_step;
+                ok[u] = col_ok && it + u < iters && ru < R;
+                if (ok[u]) {
+                    const unsigned b = ru / (unsigned)a.L, l = ru - b * (unsigned)a.L;
+                    load_vals<T, VPW, VEC>(xcol + b * a.xs_b + l * a.xs_l, v[u], n_valid);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < TAB_UNROLL; ++u) {
+                if (!ok[u]) continue;
+#pragma unroll
+                for (int j = 0; j < VPW; ++j)
+                    if (j < n_valid) range_add(acc[uniform ? 0 : j], v[u][j], sym);
+            }
+            r += TAB_UNROLL * r_step;
+        }
+        // fold the block's rows in shared memory, then one global atomic per column and block
+        const int np = uniform ? 1 : VPW;
+        if (blockDim.y > 1) {
+            for (int i = threadIdx.y * blockDim.x + threadIdx.x; i < (int)blockDim.x * VPW * 2; i += blockDim.x * blockDim.y) s_fold[i] = 0u;
+            __syncthreads();
+            for (int j = 0; j < np; ++j) {
+                atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2], acc[j].hi);
+                if (!sym) atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2 + 1], acc[j].lo);
+            }
+            __syncthreads();
+            if (threadIdx.y != 0) return;
+            for (int j = 0; j < np; ++j) { acc[j].hi = s_fold[(threadIdx.x * VPW + j) * 2]; acc[j].lo = s_fold[(threadIdx.x * VPW + j) * 2 + 1]; }
+        }
         if (uniform) {
             const long long gid = col_ok ? group_id(a, 0, 0, h, d0) : -1;
             int same;
-            __match_all_sync(0xffffffffu, gid, &same);
-            if (same) {
+            __match_all_sync(__activemask(), gid, &same);
+            if (same && __activemask() == 0xffffffffu) {
                 if (gid >= 0) {
                     Range t;
                     t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
                     t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
-                    if ((threadIdx.y * blockDim.x + threadIdx.x) % 32 == 0) stats_flush(a.stats, gid, t, sym);
+                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, sym);
                 }
             } else if (col_ok) {
                 stats_flush(a.stats, gid, acc[0], sym);
@@ -283,11 +303,47 @@ __global__ void quant_stats_kernel(QuantArgs a, int iters) {
             for (int j = 0; j < VPW; ++j)
                 if (j < n_valid) stats_flush(a.stats, group_id(a, 0, 0, h, d0 + j), acc[j], sym);
         }
+        return;
+    }
+    // ---- statistics depend on the row: flush after every row, warp-aggregated when a warp sits in one group
+    for (int it = 0; it < iters; ++it, r += r_step) {
+        const bool ok = col_ok && r < R;
+        int b = 0, l = 0;
+        if (ok) {
+            b = (int)(r / (unsigned)a.L); l = (int)(r - (unsigned)b * (unsigned)a.L);
+            float v[VPW];
+            load_vals<T, VPW, VEC>(xcol + b * a.xs_b + l * a.xs_l, v, n_valid);
+#pragma unroll
+            for (int j = 0; j < VPW; ++j)
+                if (j < n_valid) range_add(acc[uniform ? 0 : j], v[j], sym);
+        }
+        if (uniform) {
+            const long long gid = ok ? group_id(a, b, l, h, d0) : -1;
+            int same;
+            __match_all_sync(0xffffffffu, gid, &same);
+            if (same) {
+                if (gid >= 0) {
+                    Range t;
+                    t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
+                    t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
+                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, sym);
+                }
+            } else if (ok) {
+                stats_flush(a.stats, gid, acc[0], sym);
+            }
+            range_init(acc[0]);
+        } else if (ok) {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (j < n_valid) stats_flush(a.stats, group_id(a, b, l, h, d0 + j), acc[j], sym);
+                range_init(acc[j]);
+            }
+        }
     }
 }
 
 template <typename T, int STORE_BITS, bool VEC>
-__global__ void quant_apply_kernel(QuantArgs a, int iters) {
+__global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     if (cs >= a.H * a.words) return;
@@ -297,49 +353,64 @@ __global__ void quant_apply_kernel(QuantArgs a, int iters) {
     const bool sym = a.symmetric != 0;
     const bool uniform = (a.group % VPW) == 0;
     const bool row_dep = !(a.share_b && a.share_l);
-    const long long R = (long long)a.B * a.L;
-    const long long r_step = (long long)gridDim.y * blockDim.y;
+    const unsigned R = (unsigned)a.B * (unsigned)a.L;
+    const unsigned r_step = gridDim.y * blockDim.y;
     const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
     const int np = uniform ? 1 : VPW;
+    const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
     float scale[VPW], zp[VPW];
     auto fetch = [&](int b, int l) {
         for (int j = 0; j < np; ++j) {
             const int d = min(d0 + j, a.D - 1);
             const long long gid = group_id(a, b, l, h, d);
-            Range r;
-            r.hi = a.stats[gid * 2];
-            r.lo = a.stats[gid * 2 + 1];
-            params_from_range(r, a.bits, sym, a.eps, scale[j], zp[j]);
+            Range rg;
+            rg.hi = a.stats[gid * 2];
+            rg.lo = a.stats[gid * 2 + 1];
+            params_from_range(rg, a.bits, sym, a.eps, scale[j], zp[j]);
         }
     };
     if (!row_dep) fetch(0, 0);
 
-    long long r = (long long)blockIdx.y * blockDim.y + threadIdx.y;
-    for (int it = 0; it < iters && r < R; ++it, r += r_step) {
-        const int b = (int)(r / a.L), l = (int)(r % a.L);
-        if (row_dep) fetch(b, l);
-        float v[VPW];
-        load_vals<T, VPW, VEC>(reinterpret_cast<const T*>(a.x) + b * a.xs_b + l * a.xs_l + h * a.xs_h + d0, v, n_valid);
-        uint32_t word = 0;
+    unsigned r = blockIdx.y * blockDim.y + threadIdx.y;
+    for (int it = 0; it < iters; it += TAB_UNROLL, r += TAB_UNROLL * r_step) {
+        float v[TAB_UNROLL][VPW];
+        unsigned rb[TAB_UNROLL], rl[TAB_UNROLL];
+        bool ok[TAB_UNROLL];
 #pragma unroll
-        for (int j = 0; j < VPW; ++j) {
-            if (j < n_valid) {
-                const int pj = uniform ? 0 : j;
-                const int q = quantize_one(v[j], scale[pj], zp[pj], sym, bmin, bmax);
-                word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+        for (int u = 0; u < TAB_UNROLL; ++u) {
+            const unsigned ru = r + u * r_step;
+            ok[u] = it + u < iters && ru < R;
+            if (ok[u]) {
+                rb[u] = ru / (unsigned)a.L; rl[u] = ru - rb[u] * (unsigned)a.L;
+                load_vals<T, VPW, VEC>(xcol + rb[u] * a.xs_b + rl[u] * a.xs_l, v[u], n_valid);
             }
         }
-        a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
-        // one writer per group: the member with the lowest shared coordinates
-        const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
-        if (first) {
-            for (int j = 0; j < np; ++j) {
-                const int d = d0 + j;
-                if (d < a.D && (d % a.group) == 0) {
-                    const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
-                    a.scale[pi] = scale[j];
-                    if (!sym) a.zp[pi] = zp[j];
+#pragma unroll
+        for (int u = 0; u < TAB_UNROLL; ++u) {
+            if (!ok[u]) continue;
+            const int b = (int)rb[u], l = (int)rl[u];
+            if (row_dep) fetch(b, l);
+            uint32_t word = 0;
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (j < n_valid) {
+                    const int pj = uniform ? 0 : j;
+                    const int q = quantize_one(v[u][j], scale[pj], zp[pj], sym, bmin, bmax);
+                    word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+                }
+            }
+            a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
+            // one writer per group: the member with the lowest shared coordinates
+            const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
+            if (first) {
+                for (int j = 0; j < np; ++j) {
+                    const int d = d0 + j;
+                    if (d < a.D && (d % a.group) == 0) {
+                        const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
+                        a.scale[pi] = scale[j];
+                        if (!sym) a.zp[pi] = zp[j];
+                    }
                 }
             }
         }
@@ -384,6 +455,13 @@ static bool plan_rows(const QuantArgs& a, int vpw, bool vec, RowPlan& pl, int& t
         threads = 256;
         smem = 0;
     }
+    if (pl.n_gr >= 0x7fffffffLL) return false;
+    {
+        const int inner = pl.h_fast ? a.H : a.L, mid = pl.h_fast ? a.L : a.H;
+        pl.d_in = pl.ngr % inner;
+        pl.d_mid = (pl.ngr / inner) % mid;
+        pl.d_out = pl.ngr / (inner * mid);
+    }
     return threads % 32 == 0 && threads <= 256;
 }
 
@@ -417,17 +495,19 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     const long long R = (long long)a.B * a.L;
     const int gx = (cols + tx - 1) / tx;
     long long gy = (R + ty - 1) / ty;
-    const long long cap = ((long long)sm_count() * 8 + gx - 1) / gx;   // ~8 CTAs of 256 threads per SM
+    if (R >= 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack: batch x tokens exceeds 2^31");
+    const long long cap = ((long long)sm_count() * 4 + gx - 1) / gx;   // ~4 CTAs of 256 threads per SM
     if (gy > cap) gy = cap;
     if (gy < 1) gy = 1;
     if (gy > 65535) gy = 65535;
     const int iters = (int)((R + gy * ty - 1) / (gy * ty));
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
+    const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
     if (vec) {
-        quant_stats_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
+        quant_stats_kernel<T, SB, true><<<grid, block, fold, st>>>(a, iters);
         quant_apply_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
     } else {
-        quant_stats_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
+        quant_stats_kernel<T, SB, false><<<grid, block, fold, st>>>(a, iters);
         quant_apply_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
     }
     VARQ_CUDA_TRY(cudaGetLastError());
