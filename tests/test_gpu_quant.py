@@ -236,3 +236,46 @@ def test_full_size_step_properties(mode, kw):
         r = O.OracleVARQ(bits, "BLHc", mode, **kw)
         r.use_var_q(x[:2, :64].cpu())
         assert bits_equal(q.cached_item[:2, :64], r.cached_item)
+
+
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("symmetric", [True, False])
+def test_rounding_ties_and_their_neighbours(bits, symmetric):
+    """Quotients at and within a few ulps of k + 1/2, for many scales: the kernel multiplies by a
+    reciprocal and must still reproduce round-half-even of the fp32-rounded true quotient."""
+    g = torch.Generator().manual_seed(bits)
+    lo, hi = O.bounds(bits)
+    rows, c = 4096, 64
+    amax = torch.rand(rows, generator=g) * 10 ** (torch.rand(rows, generator=g) * 8 - 4)      # 1e-4 .. 1e4
+    span = float(hi) if symmetric else float((1 << bits) - 1)
+    s = amax / span
+    k = torch.randint(lo, hi, (rows, c), generator=g).float() + 0.5
+    x = (k * s[:, None]).clamp(-amax[:, None], amax[:, None])
+    ulps = torch.randint(-3, 4, (rows, c), generator=g, dtype=torch.int32)
+    x = (x.view(torch.int32) + ulps).view(torch.float32)
+    x = torch.where(x.abs() > amax[:, None], torch.sign(x) * amax[:, None], x)
+    x[:, 0] = amax                      # pins max |x| (and max) of the row
+    x[:, 1] = -amax if symmetric else 0.0 * amax
+    x = x.view(1, rows, 1, c)
+    ref = O.OracleVARQ(bits, "BLHc", "G_TOKEN_HEAD", symmetric=symmetric)
+    dut = VAR_Q(quant_bits=bits, qkv_format="BLHc", quant_method="G_TOKEN_HEAD", symmetric=symmetric)
+    want, got = ref.use_var_q(x), dut.use_var_q(x.to(DEV))
+    assert bits_equal(dut.cached_scale, ref.cached_scale)
+    assert bits_equal(dut.cached_item, ref.cached_item)
+    assert bits_equal(got, want)
+    # the same rows through the two-kernel path (per-tensor statistics)
+    ref2, dut2 = O.OracleVARQ(bits, "BLHc", "G_SCALE", symmetric=symmetric), VAR_Q(bits, "BLHc", "G_SCALE", symmetric=symmetric)
+    assert bits_equal(dut2.use_var_q(x.to(DEV)), ref2.use_var_q(x))
+    assert bits_equal(dut2.cached_item, ref2.cached_item)
+
+
+@pytest.mark.parametrize("B", [8, 16, 64])
+@pytest.mark.parametrize("bits", [2, 4, 8])
+@pytest.mark.parametrize("symmetric,group", [(True, None), (False, None), (False, 32), (True, 16)])
+def test_batch_shared_groups_register_resident_path(B, bits, symmetric, group):
+    """Batch sizes that fill every register slot of the single-pass kernel (B = lanes x vectors)."""
+    for fmt, dtype in (("BLHc", torch.float32), ("BHLc", torch.bfloat16)):
+        run_pair(fmt, "G_TOKEN_HEAD", bits, (1, 5, 12), B=B, H=4, c=64, dtype=dtype, seed=B + bits,
+                 symmetric=symmetric, group_size=group)
+    run_pair("BLHc", "G_TOKEN_HEAD", bits, (3, 4), B=B, H=2, c=128, dtype=torch.float16, seed=B, strided=True,
+             symmetric=symmetric, group_size=group)

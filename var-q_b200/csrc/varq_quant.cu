@@ -56,11 +56,21 @@ __device__ __forceinline__ void params_from_range(const Range& r, int bits, bool
     }
 }
 
-__device__ __forceinline__ int quantize_one(float x, float scale, float zp, bool symmetric, float bmin, float bmax) {
-    float r = rintf(__fdiv_rn(x, scale));
-    if (!symmetric) r = __fadd_rn(r, zp);
-    r = fminf(fmaxf(r, bmin), bmax);
-    return (int)r;
+// code = clamp(rint(x / scale) [+ zp]) with the reference's double rounding (the quotient is rounded to
+// fp32, then to an integer), without a division per element: t = x * rcp (rcp = RN(1 / scale)) is within
+// |t| * 2^-22 of the true quotient, and so is RN(x / scale); unless t lies that close to a half-integer
+// both round to the same integer.  The rare close calls, and quotients too large for the
+// add-a-magic-constant rounding, take the exact division.
+__device__ __forceinline__ int quantize_one(float x, float scale, float rcp, float zp, bool symmetric, float bmin,
+                                            float bmax) {
+    constexpr float MAGIC = 12582912.0f;                 // 1.5 * 2^23: RN(t + MAGIC) - MAGIC == rint(t) for |t| < 2^22
+    const float t = x * rcp;
+    float k = (t + MAGIC) - MAGIC;
+    const float slack = fabsf(t) * 4.8e-7f + 1e-30f;     // 2^-21 |t|: twice the bound above
+    if (fabsf(fabsf(t - k) - 0.5f) <= slack || !(fabsf(t) < 2097152.0f)) k = rintf(__fdiv_rn(x, scale));
+    if (!symmetric) k = __fadd_rn(k, zp);
+    k = fminf(fmaxf(k, bmin), bmax);
+    return __float_as_int(k + MAGIC);                    // low bits hold the two's-complement code
 }
 
 // =====================================================================================
@@ -191,15 +201,16 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
     // ---- quantize, pack, store
     const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
     float scale = 0.f, zp = 0.f;
-    if (a.share_b) params_from_range(rg[0], a.bits, sym, a.eps, scale, zp);
+    float rcp = 0.f;
+    if (a.share_b) { params_from_range(rg[0], a.bits, sym, a.eps, scale, zp); rcp = __frcp_rn(scale); }
 #pragma unroll
     for (int k = 0; k < NVMAX; ++k) {
         if (xoff[k] < 0) continue;
-        if (!a.share_b) params_from_range(rg[k], a.bits, sym, a.eps, scale, zp);
+        if (!a.share_b) { params_from_range(rg[k], a.bits, sym, a.eps, scale, zp); rcp = __frcp_rn(scale); }
         uint32_t word = 0;
 #pragma unroll
         for (int j = 0; j < VPW; ++j) {
-            const int q = quantize_one(v[k][j], scale, zp, sym, bmin, bmax);
+            const int q = quantize_one(v[k][j], scale, rcp, zp, sym, bmin, bmax);
             word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
         }
         a.codes[vb[k] * a.cs_b + vl[k] * a.cs_l + vh[k] * a.cs_h + w] = (int32_t)word;
@@ -209,6 +220,125 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
             a.scale[pi] = scale;
             if (!sym) a.zp[pi] = zp;
         }
+    }
+}
+
+
+// =====================================================================================
+// lean rows path: groups shared over the batch, every thread holds a full set of vectors
+// =====================================================================================
+// Per-group constants of the division-free quantizer.  RN(x / scale) lies strictly between
+// x * rcp_lo and x * rcp_hi (rcp_lo/hi = RN(1/scale) * (1 -/+ 2^-21)), and rint is monotonic, so
+// when both ends round to the same integer that integer is the reference's code; otherwise (about
+// once in 10^4 elements) the exact division decides.  Rounding is done by adding 1.5 * 2^23, which
+// also leaves the two's-complement code in the low mantissa bits.
+struct GroupQ {
+    float scale, zp, rcp_lo, rcp_hi, y_min, y_max;
+};
+constexpr float Q_MAGIC = 12582912.0f;
+__device__ __forceinline__ GroupQ make_group_q(float scale, float zp, int bits) {
+    GroupQ g;
+    const float rcp = __frcp_rn(scale);
+    g.scale = scale; g.zp = zp;
+    g.rcp_lo = rcp * (1.0f - 4.76837158e-7f);
+    g.rcp_hi = rcp * (1.0f + 4.76837158e-7f);
+    g.y_min = Q_MAGIC - (float)(1 << (bits - 1));
+    g.y_max = Q_MAGIC + (float)((1 << (bits - 1)) - 1);
+    return g;
+}
+template <bool SYM>
+__device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g) {
+    float y = fmaf(x, g.rcp_hi, Q_MAGIC);
+    const float y2 = fmaf(x, g.rcp_lo, Q_MAGIC);
+    bool slow = y != y2;
+    if (!SYM) slow = slow || !(fabsf(y - Q_MAGIC) < 2097152.0f);      // offset data: quotient too large for the trick
+    if (slow) {
+        float k = rintf(__fdiv_rn(x, g.scale));
+        if (!SYM) k = __fadd_rn(k, g.zp);
+        y = fminf(fmaxf(k, g.y_min - Q_MAGIC), g.y_max - Q_MAGIC) + Q_MAGIC;
+    } else if (!SYM) {
+        y = ((y - Q_MAGIC) + g.zp) + Q_MAGIC;                           // integers below 2^23: exact
+    }
+    y = fminf(fmaxf(y, g.y_min), g.y_max);
+    return __float_as_uint(y);
+}
+
+struct LeanPlan {
+    int tpr, bp, ngr, lpg, h_fast;
+    int xs_row_in, xs_row_out;     // element strides of the inner / outer coordinate of a group row
+    int cs_row_in, cs_row_out, ps_row_in, ps_row_out;
+    int n_in;                      // size of the inner coordinate (H if h_fast else L)
+    int xs_bstep, cs_bstep;        // bp * batch stride (elements / words)
+};
+
+template <typename T, int STORE_BITS, bool SYM>
+__global__ void __launch_bounds__(256) quant_rows_lean_kernel(QuantArgs a, LeanPlan pl) {
+    constexpr int VPW = 32 / STORE_BITS;
+    constexpr int NV = 32 / VPW;
+    __shared__ uint32_t s_stats[256];          // [ngr * groups per row][2]
+    const int tid = threadIdx.x;
+    const int w = tid % pl.tpr;
+    const int rest = tid / pl.tpr;
+    const int g_local = rest % pl.ngr;
+    const int bl = rest / pl.ngr;
+    const int d0 = w * VPW;
+    const int gpr = a.D / a.group;
+    const unsigned gr = blockIdx.x * (unsigned)pl.ngr + g_local;
+    const int r_in = (int)(gr % (unsigned)pl.n_in), r_out = (int)(gr / (unsigned)pl.n_in);
+    const int x0 = bl * (int)a.xs_b + r_in * pl.xs_row_in + r_out * pl.xs_row_out + d0;
+    const int c0 = bl * (int)a.cs_b + r_in * pl.cs_row_in + r_out * pl.cs_row_out + w;
+
+    if (pl.bp > 1) {
+        if (tid < pl.ngr * gpr * 2) s_stats[tid] = 0u;
+        __syncthreads();
+    }
+    float v[NV][VPW];
+    const T* xp = reinterpret_cast<const T*>(a.x) + x0;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) load_vals<T, VPW, true>(xp + k * pl.xs_bstep, v[k], VPW);
+
+    // statistics in float registers; the order-preserving integer form is only needed for the shared atomics
+    float hi = SYM ? 0.f : v[0][0], lo = v[0][0];
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) {
+            if (SYM) hi = fmaxf(hi, fabsf(v[k][j]));
+            else { hi = fmaxf(hi, v[k][j]); lo = fminf(lo, v[k][j]); }
+        }
+    for (int m = 1; m < pl.lpg; m <<= 1) {
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, m));
+        if (!SYM) lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, m));
+    }
+    Range rg;
+    rg.hi = f2ord(hi);
+    rg.lo = SYM ? 0u : ~f2ord(lo);
+    if (pl.bp > 1) {
+        const int slot = (g_local * gpr + d0 / a.group) * 2;
+        if ((w % pl.lpg) == 0) {
+            atomicMax(&s_stats[slot], rg.hi);
+            if (!SYM) atomicMax(&s_stats[slot + 1], rg.lo);
+        }
+        __syncthreads();
+        rg.hi = s_stats[slot];
+        rg.lo = s_stats[slot + 1];
+    }
+    float scale, zp;
+    params_from_range(rg, a.bits, SYM, a.eps, scale, zp);
+    const GroupQ gq = make_group_q(scale, zp, a.bits);
+    int32_t* cp = a.codes + c0;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < VPW; ++j)
+            word |= (quant_code<SYM>(v[k][j], gq) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+        cp[k * pl.cs_bstep] = (int32_t)word;
+    }
+    if (bl == 0 && (d0 % a.group) == 0) {
+        const long long pi = (long long)r_in * pl.ps_row_in + (long long)r_out * pl.ps_row_out + (long long)(d0 / a.group) * a.ps_g;
+        a.scale[pi] = scale;
+        if (!SYM) a.zp[pi] = zp;
     }
 }
 
@@ -359,7 +489,7 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
     const int np = uniform ? 1 : VPW;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
-    float scale[VPW], zp[VPW];
+    float scale[VPW], zp[VPW], rcp[VPW];
     auto fetch = [&](int b, int l) {
         for (int j = 0; j < np; ++j) {
             const int d = min(d0 + j, a.D - 1);
@@ -368,6 +498,7 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             rg.hi = a.stats[gid * 2];
             rg.lo = a.stats[gid * 2 + 1];
             params_from_range(rg, a.bits, sym, a.eps, scale[j], zp[j]);
+            rcp[j] = __frcp_rn(scale[j]);
         }
     };
     if (!row_dep) fetch(0, 0);
@@ -396,7 +527,7 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
                     const int pj = uniform ? 0 : j;
-                    const int q = quantize_one(v[u][j], scale[pj], zp[pj], sym, bmin, bmax);
+                    const int q = quantize_one(v[u][j], scale[pj], rcp[pj], zp[pj], sym, bmin, bmax);
                     word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
@@ -465,6 +596,33 @@ static bool plan_rows(const QuantArgs& a, int vpw, bool vec, RowPlan& pl, int& t
     return threads % 32 == 0 && threads <= 256;
 }
 
+// The lean kernel applies when the batch is shared, fills every register slot (B = bp * NV) and
+// all offsets fit 32 bits.
+static bool plan_lean(const QuantArgs& a, int vpw, bool vec, const RowPlan& rp, LeanPlan& lp, long long x_extent) {
+    if (!vec || !a.share_b || a.share_l || a.share_h) return false;
+    const int nv = 32 / vpw;
+    if (rp.bp * nv != a.B || rp.nv != nv) return false;
+    if (rp.n_gr % rp.ngr != 0) return false;
+    if (rp.ngr * (a.D / a.group) * 2 > 256) return false;
+    const long long c_extent = (long long)a.B * a.cs_b;
+    if (x_extent >= 0x7fffffffLL || c_extent >= 0x7fffffffLL || x_extent < 0) return false;
+    lp.tpr = rp.tpr; lp.bp = rp.bp; lp.ngr = rp.ngr; lp.lpg = rp.lpg; lp.h_fast = rp.h_fast;
+    if (rp.h_fast) {
+        lp.n_in = a.H;
+        lp.xs_row_in = (int)a.xs_h; lp.xs_row_out = (int)a.xs_l;
+        lp.cs_row_in = (int)a.cs_h; lp.cs_row_out = (int)a.cs_l;
+        lp.ps_row_in = (int)a.ps_h; lp.ps_row_out = (int)a.ps_r;
+    } else {
+        lp.n_in = a.L;
+        lp.xs_row_in = (int)a.xs_l; lp.xs_row_out = (int)a.xs_h;
+        lp.cs_row_in = (int)a.cs_l; lp.cs_row_out = (int)a.cs_h;
+        lp.ps_row_in = (int)a.ps_r; lp.ps_row_out = (int)a.ps_h;
+    }
+    lp.xs_bstep = rp.bp * (int)a.xs_b;
+    lp.cs_bstep = rp.bp * (int)a.cs_b;
+    return true;
+}
+
 template <typename T, int SB>
 static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes, cudaStream_t st) {
     QuantArgs a = a0;
@@ -476,6 +634,15 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
         const long long per_cta = a.share_b ? pl.ngr : (long long)pl.ngr * pl.nv;
         const long long blocks = (pl.n_gr + per_cta - 1) / per_cta;
         if (blocks > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack: tensor too large");
+        LeanPlan lp;
+        const long long x_extent = (long long)(a.B - 1) * a.xs_b + (long long)(a.L - 1) * a.xs_l + (long long)(a.H - 1) * a.xs_h + a.D;
+        if (plan_lean(a, VPW, vec, pl, lp, x_extent)) {
+            if (a.symmetric) quant_rows_lean_kernel<T, SB, true><<<(unsigned)blocks, threads, 0, st>>>(a, lp);
+            else             quant_rows_lean_kernel<T, SB, false><<<(unsigned)blocks, threads, 0, st>>>(a, lp);
+            VARQ_CUDA_TRY(cudaGetLastError());
+            count_launches(1);
+            return VARQ_OK;
+        }
         quant_rows_kernel<T, SB><<<(unsigned)blocks, threads, smem, st>>>(a, pl);
         VARQ_CUDA_TRY(cudaGetLastError());
         count_launches(1);
