@@ -56,21 +56,44 @@ __device__ __forceinline__ void params_from_range(const Range& r, int bits, bool
     }
 }
 
-// code = clamp(rint(x / scale) [+ zp]) with the reference's double rounding (the quotient is rounded to
-// fp32, then to an integer), without a division per element: t = x * rcp (rcp = RN(1 / scale)) is within
-// |t| * 2^-22 of the true quotient, and so is RN(x / scale); unless t lies that close to a half-integer
-// both round to the same integer.  The rare close calls, and quotients too large for the
-// add-a-magic-constant rounding, take the exact division.
-__device__ __forceinline__ int quantize_one(float x, float scale, float rcp, float zp, bool symmetric, float bmin,
-                                            float bmax) {
-    constexpr float MAGIC = 12582912.0f;                 // 1.5 * 2^23: RN(t + MAGIC) - MAGIC == rint(t) for |t| < 2^22
-    const float t = x * rcp;
-    float k = (t + MAGIC) - MAGIC;
-    const float slack = fabsf(t) * 4.8e-7f + 1e-30f;     // 2^-21 |t|: twice the bound above
-    if (fabsf(fabsf(t - k) - 0.5f) <= slack || !(fabsf(t) < 2097152.0f)) k = rintf(__fdiv_rn(x, scale));
-    if (!symmetric) k = __fadd_rn(k, zp);
-    k = fminf(fmaxf(k, bmin), bmax);
-    return __float_as_int(k + MAGIC);                    // low bits hold the two's-complement code
+// Per-group constants of the division-free quantizer.  RN(x / scale) lies strictly between
+// x * rcp_lo and x * rcp_hi (rcp_lo/hi = RN(1/scale) * (1 -/+ 2^-21)), and rint is monotonic, so
+// when both ends round to the same integer that integer is the reference's code; otherwise (about
+// once in 10^4 elements) the exact division decides.  Rounding is done by adding 1.5 * 2^23, which
+// also leaves the two's-complement code in the low mantissa bits.
+struct GroupQ {
+    float scale, zp, rcp_lo, rcp_hi, y_min, y_max;
+};
+constexpr float Q_MAGIC = 12582912.0f;
+__device__ __forceinline__ GroupQ make_group_q(float scale, float zp, int bits) {
+    GroupQ g;
+    const float rcp = __frcp_rn(scale);
+    g.scale = scale; g.zp = zp;
+    g.rcp_lo = rcp * (1.0f - 4.76837158e-7f);
+    g.rcp_hi = rcp * (1.0f + 4.76837158e-7f);
+    g.y_min = Q_MAGIC - (float)(1 << (bits - 1));
+    g.y_max = Q_MAGIC + (float)((1 << (bits - 1)) - 1);
+    return g;
+}
+template <bool SYM>
+__device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g) {
+    float y = fmaf(x, g.rcp_hi, Q_MAGIC);
+    const float y2 = fmaf(x, g.rcp_lo, Q_MAGIC);
+    bool slow = y != y2;
+    if (!SYM) slow = slow || !(fabsf(y - Q_MAGIC) < 2097152.0f);      // offset data: quotient too large for the trick
+    if (slow) {
+        float k = rintf(__fdiv_rn(x, g.scale));
+        if (!SYM) k = __fadd_rn(k, g.zp);
+        y = fminf(fmaxf(k, g.y_min - Q_MAGIC), g.y_max - Q_MAGIC) + Q_MAGIC;
+    } else if (!SYM) {
+        y = ((y - Q_MAGIC) + g.zp) + Q_MAGIC;                           // integers below 2^23: exact
+    }
+    y = fminf(fmaxf(y, g.y_min), g.y_max);
+    return __float_as_uint(y);
+}
+
+__device__ __forceinline__ uint32_t quant_code_rt(float x, const GroupQ& g, bool sym) {
+    return sym ? quant_code<true>(x, g) : quant_code<false>(x, g);
 }
 
 // =====================================================================================
@@ -199,19 +222,17 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
     }
 
     // ---- quantize, pack, store
-    const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
     float scale = 0.f, zp = 0.f;
-    float rcp = 0.f;
-    if (a.share_b) { params_from_range(rg[0], a.bits, sym, a.eps, scale, zp); rcp = __frcp_rn(scale); }
+    GroupQ gq = make_group_q(1.f, 0.f, a.bits);
+    if (a.share_b) { params_from_range(rg[0], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp, a.bits); }
 #pragma unroll
     for (int k = 0; k < NVMAX; ++k) {
         if (xoff[k] < 0) continue;
-        if (!a.share_b) { params_from_range(rg[k], a.bits, sym, a.eps, scale, zp); rcp = __frcp_rn(scale); }
+        if (!a.share_b) { params_from_range(rg[k], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp, a.bits); }
         uint32_t word = 0;
 #pragma unroll
         for (int j = 0; j < VPW; ++j) {
-            const int q = quantize_one(v[k][j], scale, rcp, zp, sym, bmin, bmax);
-            word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+            word |= (quant_code_rt(v[k][j], gq, sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
         }
         a.codes[vb[k] * a.cs_b + vl[k] * a.cs_l + vh[k] * a.cs_h + w] = (int32_t)word;
         const bool writer = (d0 % a.group) == 0 && (a.share_b ? (vb[k] == 0) : true);
@@ -227,42 +248,6 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
 // =====================================================================================
 // lean rows path: groups shared over the batch, every thread holds a full set of vectors
 // =====================================================================================
-// Per-group constants of the division-free quantizer.  RN(x / scale) lies strictly between
-// x * rcp_lo and x * rcp_hi (rcp_lo/hi = RN(1/scale) * (1 -/+ 2^-21)), and rint is monotonic, so
-// when both ends round to the same integer that integer is the reference's code; otherwise (about
-// once in 10^4 elements) the exact division decides.  Rounding is done by adding 1.5 * 2^23, which
-// also leaves the two's-complement code in the low mantissa bits.
-struct GroupQ {
-    float scale, zp, rcp_lo, rcp_hi, y_min, y_max;
-};
-constexpr float Q_MAGIC = 12582912.0f;
-__device__ __forceinline__ GroupQ make_group_q(float scale, float zp, int bits) {
-    GroupQ g;
-    const float rcp = __frcp_rn(scale);
-    g.scale = scale; g.zp = zp;
-    g.rcp_lo = rcp * (1.0f - 4.76837158e-7f);
-    g.rcp_hi = rcp * (1.0f + 4.76837158e-7f);
-    g.y_min = Q_MAGIC - (float)(1 << (bits - 1));
-    g.y_max = Q_MAGIC + (float)((1 << (bits - 1)) - 1);
-    return g;
-}
-template <bool SYM>
-__device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g) {
-    float y = fmaf(x, g.rcp_hi, Q_MAGIC);
-    const float y2 = fmaf(x, g.rcp_lo, Q_MAGIC);
-    bool slow = y != y2;
-    if (!SYM) slow = slow || !(fabsf(y - Q_MAGIC) < 2097152.0f);      // offset data: quotient too large for the trick
-    if (slow) {
-        float k = rintf(__fdiv_rn(x, g.scale));
-        if (!SYM) k = __fadd_rn(k, g.zp);
-        y = fminf(fmaxf(k, g.y_min - Q_MAGIC), g.y_max - Q_MAGIC) + Q_MAGIC;
-    } else if (!SYM) {
-        y = ((y - Q_MAGIC) + g.zp) + Q_MAGIC;                           // integers below 2^23: exact
-    }
-    y = fminf(fmaxf(y, g.y_min), g.y_max);
-    return __float_as_uint(y);
-}
-
 struct LeanPlan {
     int tpr, bp, ngr, lpg, h_fast;
     int xs_row_in, xs_row_out;     // element strides of the inner / outer coordinate of a group row
@@ -485,11 +470,11 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
     const bool row_dep = !(a.share_b && a.share_l);
     const unsigned R = (unsigned)a.B * (unsigned)a.L;
     const unsigned r_step = gridDim.y * blockDim.y;
-    const float bmin = -(float)(1 << (a.bits - 1)), bmax = (float)((1 << (a.bits - 1)) - 1);
     const int np = uniform ? 1 : VPW;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
-    float scale[VPW], zp[VPW], rcp[VPW];
+    float scale[VPW], zp[VPW];
+    GroupQ gq[VPW];
     auto fetch = [&](int b, int l) {
         for (int j = 0; j < np; ++j) {
             const int d = min(d0 + j, a.D - 1);
@@ -498,7 +483,7 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             rg.hi = a.stats[gid * 2];
             rg.lo = a.stats[gid * 2 + 1];
             params_from_range(rg, a.bits, sym, a.eps, scale[j], zp[j]);
-            rcp[j] = __frcp_rn(scale[j]);
+            gq[j] = make_group_q(scale[j], zp[j], a.bits);
         }
     };
     if (!row_dep) fetch(0, 0);
@@ -527,8 +512,7 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
                     const int pj = uniform ? 0 : j;
-                    const int q = quantize_one(v[u][j], scale[pj], rcp[pj], zp[pj], sym, bmin, bmax);
-                    word |= ((uint32_t)q & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+                    word |= (quant_code_rt(v[u][j], gq[pj], sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
             a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
