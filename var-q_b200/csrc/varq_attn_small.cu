@@ -351,10 +351,12 @@ template <int KB, int VB>
 static int launch_small(const AttnArgs& a, cudaStream_t st) {
     const size_t smem = attn_small_smem(a);
     if (smem > 200 * 1024) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: head_dim %d needs %zu bytes of shared memory", a.D, smem);
-    static bool configured = false;   // per instantiation; attribute is sticky per function
-    if (!configured || smem > 48 * 1024) {
+    static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
+    int dev = 0;
+    VARQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_small_kernel<KB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int nqt = (a.Lq + A1_QT - 1) / A1_QT;
     if (nqt > 65535 || (long long)a.B * a.H > 65535)

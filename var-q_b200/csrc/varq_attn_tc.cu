@@ -5,10 +5,10 @@
 //              tile's keys; they read S from TMEM, apply the per-key scale / zero-point of K,
 //              do the online softmax with lazy rescaling of O, write P (fp16) to shared memory,
 //              and at the end normalise and store;
-//   warps 8-11 producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
+//   warps 8-11 (K) and 12-14 (V) producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
 //              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
 //              K as exact fp16 integer codes, V as fp16 (code - zp) * scale;
-//   warp  12   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
+//   warp  15   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
 //              O += P V, and commits completion to mbarriers.
 // Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
 // no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
@@ -20,7 +20,8 @@
 
 namespace varq {
 
-constexpr int TC_THREADS = 416;   // 8 softmax warps, 4 producer warps, 1 MMA warp
+constexpr int TC_THREADS = 512;   // 8 softmax warps, 4 K-producer warps, 3 V-producer warps, 1 MMA warp
+constexpr int TC_VPROD = 96;      // V-producer threads
 constexpr int TC_M = 128;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
 
@@ -148,7 +149,7 @@ template <int D, int NQ> struct TcPlan {
     static constexpr int OFF_PK = OFF_P + 2 * P_BYTES;        // [2][K, V]
     static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
     static constexpr int OFF_BAR = OFF_KS + 4 * 6 * N * 4;    // mbarriers
-    static constexpr int N_BARS = 17;
+    static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
     static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][2][2][128]: row halves exchange (parity, slot, half, row)
     static constexpr int TOTAL = OFF_XCH + 2 * 2 * 2 * 128 * 4;
@@ -199,14 +200,14 @@ template <> struct Codes<2> {   // one word -> 16 halves
 
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS>
-__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid) {
+__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128) {
     constexpr int VPW = 32 / BITS;            // codes per word
     constexpr int HW = VPW / 2;               // 32-bit half2 registers per word
     const int ipr = W >> 2;                   // 16-byte items per key row
     const int ishift = __ffs(ipr) - 1;
     const int items = N * ipr;
 #pragma unroll 2
-    for (int it = ptid; it < items; it += 128) {
+    for (int it = ptid; it < items; it += nthr) {
         const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
         uint4 pk = make_uint4(0u, 0u, 0u, 0u);
         uint32_t h[4 * HW];
@@ -252,11 +253,11 @@ __device__ __forceinline__ void put_word(unsigned char* tile, int key, int w, ui
 
 template <int BITS, bool EXACT>
 __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
-                                             int ptid, const ParamView& pv, int b, int h, int k0) {
+                                             int ptid, const ParamView& pv, int b, int h, int k0, int nthr = 128) {
     constexpr int VPW = 32 / BITS;
     const int total = N * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
-    for (int idx = ptid; idx < total; idx += 128) {
+    for (int idx = ptid; idx < total; idx += nthr) {
         const int key = idx >> wshift, w = idx & (W - 1);
         uint32_t word = 0;
         float s = 0.f, z = 0.f;
@@ -337,7 +338,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
-    uint64_t* bar_pk = bars;          // [2] packed K+V rows landed (tx bytes)
+    uint64_t* bar_pk = bars;          // [2] packed K rows landed (tx bytes)
     uint64_t* bar_k = bars + 2;       // [2] K operand tile and per-key tables written (128 producers)
     uint64_t* bar_v = bars + 4;       // [2] V operand tile written (128 producers)
     uint64_t* bar_s = bars + 6;       // [2] S = Q K^T complete (tcgen05.commit): K stage free again
@@ -345,6 +346,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     uint64_t* bar_pv = bars + 10;     // [2] O += P V complete (tcgen05.commit): V stage and P buffer free
     uint64_t* bar_o = bars + 12;      // all MMAs complete
     uint64_t* bar_t = bars + 13;      // [4] per-key tables of tile j written (slot j % 4; 128 producers)
+    uint64_t* bar_pkv = bars + 17;    // [2] packed V rows landed (tx bytes)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
 
@@ -358,8 +360,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_pk[i], 1);
+            mbar_init(&bar_pkv[i], 1);
             mbar_init(&bar_k[i], 128);
-            mbar_init(&bar_v[i], 128);
+            mbar_init(&bar_v[i], TC_VPROD);
             mbar_init(&bar_s[i], 1);
             mbar_init(&bar_p[i], 256);
             mbar_init(&bar_pv[i], 1);
@@ -369,7 +372,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 12) {   // TMEM allocation by one full warp
+    if (warp == 15) {   // TMEM allocation by one full warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -548,15 +551,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         tc_fence_before();
     } else if (warp < 12) {
-        // =============================================================== producers
+        // =============================================================== K producers (and per-key tables)
         const int ptid = tid - 256;
         auto issue = [&](int j) {
             const int s = j & 1;
-            const int n_valid = min(N, a.Lk - j * N);
-            const uint32_t kbytes = (uint32_t)n_valid * wk * 4, vbytes = (uint32_t)n_valid * wv * 4;
-            mbar_expect_tx(&bar_pk[s], kbytes + vbytes);
+            const uint32_t kbytes = (uint32_t)min(N, a.Lk - j * N) * wk * 4;
+            mbar_expect_tx(&bar_pk[s], kbytes);
             bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)j * N * wk, kbytes, &bar_pk[s]);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, vbytes, &bar_pk[s]);
         };
         if (ptid == 0) {
             issue(0);
@@ -584,8 +585,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         fetch_params(0);
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
-            const int k0 = j * N;
-            const int n_valid = min(N, a.Lk - k0);
+            const int n_valid = min(N, a.Lk - j * N);
             if (warp == 8) TC_TRACE(2, j, 0);
             const float sc = nsc, zs = nzs, vsc = nvsc, vzp = nvzp;
             const float bias = (ptid < n_valid) ? 0.f : -1e30f;
@@ -595,14 +595,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
             if (warp == 8) TC_TRACE(2, j, 2);
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
-            const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             unsigned char* tk = smem + P::OFF_K + s * P::KV_BYTES;
-            unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
             if (ok) {
                 if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
                 else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
                 else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
-                if (warp == 8) TC_TRACE(2, j, 6);
+                if (warp == 8) TC_TRACE(2, j, 3);
                 if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
                     float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 6 * N;
                     const float scl = sc * a.scale_log2;
@@ -617,24 +615,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 mbar_arrive(&bar_k[s]);
                 mbar_arrive(&bar_t[j & 3]);
             }
-            if (warp == 8) TC_TRACE(2, j, 3);
-            if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
             if (warp == 8) TC_TRACE(2, j, 4);
-            if (ok) {
-                if (v_exact) {
-                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid);
-                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid);
-                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid);
-                } else {
-                    if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-                    else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-                    else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0);
-                }
-                fence_async_smem();
-                mbar_arrive(&bar_v[s]);
-            }
-            if (warp == 8) TC_TRACE(2, j, 5);
-            {   // every producer is done with the packed stage; all 128 take the same decision on `ok`
+            {   // every K producer is done with the packed stage; all 128 take the same decision on `ok`
                 uint32_t all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                              : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
@@ -648,6 +630,61 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             for (int j = 0; j < issued; ++j) {
                 bool landed = false;
                 for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pk[j & 1], (j >> 1) & 1);
+            }
+        }
+    } else if (warp < 15) {
+        // =============================================================== V producers
+        const int ptid = tid - 384;
+        auto issue = [&](int j) {
+            const int s = j & 1;
+            const uint32_t vbytes = (uint32_t)min(N, a.Lk - j * N) * wv * 4;
+            mbar_expect_tx(&bar_pkv[s], vbytes);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, vbytes, &bar_pkv[s]);
+        };
+        if (ptid == 0) {
+            issue(0);
+            if (T > 1) issue(1);
+        }
+        bool ok = true;
+        int issued = min(T, 2);
+        const bool v_exact = a.vp.group == D;
+        for (int j = 0; j < T; ++j) {
+            const int s = j & 1;
+            const int k0 = j * N;
+            const int n_valid = min(N, a.Lk - k0);
+            ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
+            if (warp == 12) TC_TRACE(2, j, 5);
+            if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
+            if (warp == 12) TC_TRACE(2, j, 6);
+            const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
+            unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
+            if (ok) {
+                if (v_exact) {
+                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
+                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
+                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
+                } else {
+                    if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                }
+                fence_async_smem();
+                mbar_arrive(&bar_v[s]);
+            }
+            if (warp == 12) TC_TRACE(2, j, 7);
+            {
+                uint32_t all_ok;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
+                ok = all_ok != 0;
+            }
+            if (!ok) break;
+            if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
+        }
+        if (!ok && ptid == 0) {
+            for (int j = 0; j < issued; ++j) {
+                bool landed = false;
+                for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pkv[j & 1], (j >> 1) & 1);
             }
         }
     } else if (lane == 0) {
@@ -710,7 +747,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 12) {
+    if (warp == 15) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
     }
@@ -732,7 +769,13 @@ static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
     using P = TcPlan<D, NQ>;
     static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
     const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
-    VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
+    int dev = 0;
+    VARQ_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
     const int nqt = (a.Lq + TC_M - 1) / TC_M;
     if ((long long)a.B * a.H > 65535) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: batch x heads > 65535");
     dim3 grid(nqt, a.B * a.H);
