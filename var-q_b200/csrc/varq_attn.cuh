@@ -23,6 +23,29 @@ __device__ __forceinline__ float load_q_elem(const void* q, int dtype, long long
     if (dtype == VARQ_F16) return __half2float(__ldg(reinterpret_cast<const __half*>(q) + off));
     return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(q) + off));
 }
+// eight consecutive elements starting at element `off`; 16-byte loads when the address allows
+__device__ __forceinline__ void load_q8(const void* q, int dtype, long long off, float (&v)[8]) {
+    const int es = dtype == VARQ_F32 ? 4 : 2;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(q) + (unsigned long long)off * es;
+    if (addr & 15u) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = load_q_elem(q, dtype, off + j);
+    } else if (dtype == VARQ_F32) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(addr)), b = __ldg(reinterpret_cast<const float4*>(addr) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(addr));
+        if (dtype == VARQ_F16) {
+            const __half* e = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __half2float(e[j]);
+        } else {
+            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(e[j]);
+        }
+    }
+}
 __device__ __forceinline__ void store_o_elem(void* o, int dtype, long long off, float v) {
     if (dtype == VARQ_F32) reinterpret_cast<float*>(o)[off] = v;
     else if (dtype == VARQ_F16) reinterpret_cast<__half*>(o)[off] = __float2half_rn(v);

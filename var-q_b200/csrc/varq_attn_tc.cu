@@ -114,6 +114,13 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+__device__ __forceinline__ void sts128(void* p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    *reinterpret_cast<uint4*>(p) = make_uint4(x, y, z, w);
+}
+__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ float pick(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 format:
 // [0,14) start >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4 |
 // [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
@@ -152,7 +159,8 @@ template <int D, int NQ> struct TcPlan {
     static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
     static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][2][2][128]: row halves exchange (parity, slot, half, row)
-    static constexpr int TOTAL = OFF_XCH + 2 * 2 * 2 * 128 * 4;
+    static constexpr int OFF_QSUM = OFF_XCH + 2 * 2 * 2 * 128 * 4;   // float [128]: row sums of Q (zero-point term of K)
+    static constexpr int TOTAL = OFF_QSUM + 128 * 4;
     static constexpr int TMEM_COLS = (2 * N + D) <= 256 ? 256 : 512;
     static constexpr int COL_S = 0, COL_O = 2 * N;
 };
@@ -200,19 +208,22 @@ template <> struct Codes<2> {   // one word -> 16 halves
 
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS>
-__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128) {
+__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
+                                           int rows = -1) {
+    // rows [n_valid, rows) are zero-filled; consumers never read past `rows`
+    if (rows < 0) rows = N;
     constexpr int VPW = 32 / BITS;            // codes per word
     constexpr int HW = VPW / 2;               // 32-bit half2 registers per word
     const int ipr = W >> 2;                   // 16-byte items per key row
     const int ishift = __ffs(ipr) - 1;
-    const int items = N * ipr;
+    const int items = rows * ipr;
 #pragma unroll 2
     for (int it = ptid; it < items; it += nthr) {
         const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
         uint4 pk = make_uint4(0u, 0u, 0u, 0u);
         uint32_t h[4 * HW];
         if (key < n_valid) {
-            pk = *reinterpret_cast<const uint4*>(packed + key * W + wi);
+            pk = lds128(packed + key * W + wi);
             Codes<BITS>::cvt(pk.x, h);
             Codes<BITS>::cvt(pk.y, h + HW);
             Codes<BITS>::cvt(pk.z, h + 2 * HW);
@@ -226,7 +237,7 @@ __device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* 
         const int ch0 = (d0 & 63) >> 3;
 #pragma unroll
         for (int c = 0; c < HW; ++c)         // HW chunks of 8 halves
-            *reinterpret_cast<uint4*>(row + (((ch0 + c) ^ (key & 7)) << 4)) = make_uint4(h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
@@ -255,7 +266,7 @@ template <int BITS, bool EXACT>
 __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
                                              int ptid, const ParamView& pv, int b, int h, int k0, int nthr = 128) {
     constexpr int VPW = 32 / BITS;
-    const int total = N * W;
+    const int total = min(N, (n_valid + 31) & ~31) * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
     for (int idx = ptid; idx < total; idx += nthr) {
         const int key = idx >> wshift, w = idx & (W - 1);
@@ -278,7 +289,6 @@ __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t
 // b2 = b1 + log2(V scale), kzs = K zero-point * ks, vinv = 1 / V scale, vz = V zero-point.
 // four consecutive table entries with one 16-byte shared-memory load (tables are 16-byte aligned)
 __device__ __forceinline__ float4 tab4(const float* p, int c) { return *reinterpret_cast<const float4*>(p + c); }
-__device__ __forceinline__ float pick(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 template <bool KZ>
 __device__ __forceinline__ float softmax_max32(const uint32_t (&raw)[32], const float* ks, const float* b1,
@@ -314,8 +324,16 @@ __device__ __forceinline__ void softmax_exp32(const uint32_t (&raw)[32], uint32_
             float x0 = fmaf(__uint_as_float(raw[c + i]), pick(s4, i), pick(b4, i));
             float x1 = fmaf(__uint_as_float(raw[c + i + 1]), pick(s4, i + 1), pick(b4, i + 1));
             if (KZ) { x0 = fmaf(-pick(z4, i), qsum, x0); x1 = fmaf(-pick(z4, i + 1), qsum, x1); }
+#if defined(VARQ_ABL_NOEX2)
+            const __half2 h2 = __floats2half2_rn(x0 - m_used, x1 - m_used);
+#else
             const __half2 h2 = __floats2half2_rn(ex2(x0 - m_used), ex2(x1 - m_used));
+#endif
+#if defined(VARQ_ABL_NOCVT)
+            const float2 pf = make_float2(x0, x1);
+#else
             const float2 pf = __half22float2(h2);           // the rounded values feed the normaliser too
+#endif
             if (VX) {
                 l0 = fmaf(pf.x, pick(i4, i), l0);
                 l1 = fmaf(pf.y, pick(i4, i + 1), l1);
@@ -357,6 +375,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int T = (a.Lk + N - 1) / N;
     const int wk = a.wk, wv = a.wv;
 
+    const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
+    const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
+    if (warp == 0) TC_TRACE(3, 30, 0);
+    const int aq = (nq + 31) >> 5;                  // TMEM lane quarters that hold real queries
+    float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
+
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_pk[i], 1);
@@ -364,46 +388,65 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             mbar_init(&bar_k[i], 128);
             mbar_init(&bar_v[i], TC_VPROD);
             mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_p[i], 256);
+            mbar_init(&bar_p[i], 64 * aq);          // only the warps that own real query rows take part
             mbar_init(&bar_pv[i], 1);
         }
         mbar_init(bar_o, 1);
         for (int i = 0; i < 4; ++i) mbar_init(&bar_t[i], 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first two packed tiles are requested right away; their latency overlaps the rest of the set-up
+        for (int j = 0; j < 2 && j < T; ++j) {
+            const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
+            mbar_expect_tx(&bar_pk[j], rows * wk * 4);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
+            mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
+        }
     }
+    if (tid < 128) s_qsum[tid] = 0.f;
     if (warp == 15) {   // TMEM allocation by one full warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // ---- Q tile -> shared (fp16 hi [, lo]), all threads
-    {
-        constexpr int CH = D / 8;   // 16-byte chunks per row
-        for (int i = tid; i < TC_M * CH; i += TC_THREADS) {
-            const int r = i / CH, c = i - r * CH;
-            __half hi[8], lo[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float v = 0.f;
-                if (r < nq) v = load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8 + j);
-                hi[j] = __float2half_rn(v);
-                lo[j] = __float2half_rn(v - __half2float(hi[j]));
-            }
-            const uint32_t off = tile_off(r, c * 8, TC_M);
-            *reinterpret_cast<uint4*>(smem + P::OFF_Q + off) = *reinterpret_cast<uint4*>(hi);
-            if constexpr (NQ == 2) *reinterpret_cast<uint4*>(smem + P::OFF_Q + P::Q_BYTES + off) = *reinterpret_cast<uint4*>(lo);
-        }
-    }
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (warp == 0) TC_TRACE(3, 30, 1);
 
-    const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
-    const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
+    if (warp < 8 || warp == 15) {
+        // ---- Q tile -> shared (fp16 hi [, lo]) by the softmax and MMA warps; the producers are already at work
+        constexpr int CH = D / 8;   // 16-byte chunks per row
+        const int qtid = warp < 8 ? tid : 256 + lane;
+        const bool want_qsum = a.kp.zp != nullptr;
+        for (int i = qtid; i < TC_M * CH; i += 288) {
+            const int r = i / CH, c = i - r * CH;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.f;
+            if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v);
+            __half hi[8], lo[8];
+            float part = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                hi[j] = __float2half_rn(v[j]);
+                lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+                part += v[j];
+            }
+            const uint32_t off = tile_off(r, c * 8, TC_M);
+            *reinterpret_cast<uint4*>(smem + P::OFF_Q + off) = *reinterpret_cast<uint4*>(hi);
+            if constexpr (NQ == 2) *reinterpret_cast<uint4*>(smem + P::OFF_Q + P::Q_BYTES + off) = *reinterpret_cast<uint4*>(lo);
+            if (want_qsum && r < nq) atomicAdd(&s_qsum[r], part);
+        }
+        fence_async_smem();
+        asm volatile("bar.sync 7, 288;" ::: "memory");
+        if (warp == 0) TC_TRACE(3, 30, 2);
+    }
 
-    if (warp < 8) {
+    if (warp < 8 && (warp & 3) >= aq) {
+        // this warp's TMEM lanes hold no real query: nothing to do until the tear-down
+    } else if (warp < 8) {
         // =============================================================== softmax / epilogue
         constexpr int NH = N / 2;                           // keys per thread and tile
         constexpr int DH = D / 2;                           // output columns per thread
@@ -421,10 +464,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const bool v_exact = a.vp.group == D;               // V scale constant along head_dim: folded into P
         const bool v_zp = v_exact && a.vp.zp != nullptr;
         const bool k_zp = a.kp.zp != nullptr;
-        float qsum = 0.f;
-        if (k_zp && r < nq) {
-            for (int d = 0; d < D; ++d) qsum += load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + d);
-        }
+        const float qsum = k_zp ? s_qsum[r] : 0.f;
         float m_used = -FLT_MAX, l_run = 0.f, corr = 0.f;
         bool ok = true;
         for (int j = 0; j < T; ++j) {
@@ -516,7 +556,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     const int ch0 = (col & 63) >> 3;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
-                        *reinterpret_cast<uint4*>(blk + (((ch0 + q4) ^ (r & 7)) << 4)) = make_uint4(ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
+                        sts128(blk + (((ch0 + q4) ^ (r & 7)) << 4), ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
                 }
                 fence_async_smem();
                 tc_fence_before();
@@ -529,6 +569,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         fin[half * 128 + r] = l_run;
         fin[512 + half * 128 + r] = corr;
         ok = ok && mbar_wait(bar_o, 0, abort_flag, 14);
+        if (warp == 0) TC_TRACE(3, 30, 3);
         ok = __all_sync(0xffffffffu, ok);
         ok = pair_sync_and(ok);
         if (ok) {
@@ -559,12 +600,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             mbar_expect_tx(&bar_pk[s], kbytes);
             bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)j * N * wk, kbytes, &bar_pk[s]);
         };
-        if (ptid == 0) {
-            issue(0);
-            if (T > 1) issue(1);
-        }
         bool ok = true;
-        int issued = min(T, 2);
+        int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
         const bool v_exact = a.vp.group == D;
         // per-key parameters of a tile are fetched one tile ahead so the global-load latency is hidden
         float nsc = 0.f, nzs = 0.f, nvsc = 1.f, nvzp = 0.f;
@@ -641,12 +678,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             mbar_expect_tx(&bar_pkv[s], vbytes);
             bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, vbytes, &bar_pkv[s]);
         };
-        if (ptid == 0) {
-            issue(0);
-            if (T > 1) issue(1);
-        }
         bool ok = true;
-        int issued = min(T, 2);
+        int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
         const bool v_exact = a.vp.group == D;
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
@@ -657,12 +690,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
             if (warp == 12) TC_TRACE(2, j, 6);
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
+            const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
             unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
             if (ok) {
                 if (v_exact) {
-                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
-                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
-                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD);
+                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                 } else {
                     if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
                     else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
@@ -700,10 +734,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), N * 128, 1024);
         auto issue_pv = [&](int j) {
             const int s = j & 1;
+            const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
             const uint64_t pd = pd0 + (uint64_t)((s * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
 #pragma unroll
             for (int kk = 0; kk < N / 16; ++kk)
-                tc_mma_f16(tmem_base + P::COL_O, pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                if (kk < ksteps) tc_mma_f16(tmem_base + P::COL_O, pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
                            vd + (uint64_t)((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
             tc_commit(&bar_pv[s]);
         };
@@ -746,7 +781,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         tc_fence_before();
     }
+    if (warp == 0) TC_TRACE(3, 30, 4);
     __syncthreads();
+    if (warp == 0) TC_TRACE(3, 30, 5);
     if (warp == 15) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
