@@ -241,18 +241,32 @@ def run_ours(args):
     clocks = sampler.stop()
     ms = t0.elapsed_time(t1)
 
-    # ---- the dominant kernel, timed launch by launch in an eager pass over the same steps
-    probes = []
-    def probe_top(kind, si):
-        if (kind, si) != top:
-            return None
-        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-        probes.append(ev)
-        return ev
-    for _ in range(min(args.steps, 5)):
-        hot_path_step(inputs, probe_top)
+    # ---- the dominant kernel alone: back-to-back launches on the state it sees in the step, so that
+    # the CUDA events measure the kernel and not the Python between launches
+    from VAR_Q.attention import attend_cached
+    kind, si = top
+    kq, vq = new_quantizers()[0]
+    for rec in inputs[:si]:
+        kq.append(rec["k"]); vq.append(rec["v"])
+    rec = inputs[si]
+    if kind == "attn":
+        kq.append(rec["k"]); vq.append(rec["v"])
+        launch = lambda: attend_cached(rec["q"], kq, vq, 1.0, out_dtype=torch.bfloat16)
+    elif kind == "quant_k":
+        launch = lambda: kq.quant(rec["k"])          # re-quantizes the pending step in place
+    else:
+        launch = lambda: vq.quant(rec["v"])
+    reps = 20
+    for _ in range(3):
+        launch()
     torch.cuda.synchronize()
-    top_ms = statistics.mean(a.elapsed_time(b) for a, b in probes)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(reps):
+        launch()
+    k1.record()
+    torch.cuda.synchronize()
+    top_ms = k0.elapsed_time(k1) / reps
 
     # ---- end to end with host buffers
     dev_bufs = [{"q": torch.empty_like(r["q"]), "k": torch.empty_like(r["k"]), "qkv16": torch.empty_like(r["qkv16"])} for r in inputs]
@@ -293,7 +307,7 @@ def run_ours(args):
             roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
         roof.update({"traffic": None, "kernel": f"{kind}[scale {si}: l={lq}, cached={lk}]", "launch_ms": top_ms,
                      "share_of_step": share[top] / sum(share.values()), "peak_source": peaks["source"],
-                     "timing": "CUDA events around each launch of this kernel in an eager pass of the same steps",
+                     "timing": "CUDA events around 20 back-to-back launches of this kernel on the step's own state",
                      "algorithmic_bytes": nbytes, "algorithmic_flops": flops})
         value = world * IMAGES * args.steps / (ms * 1e-3)
         line = {
