@@ -383,6 +383,36 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_case(name):
+    """One kernel on a small, larger-than-L2 case, a few launches: the command ncu captures."""
+    from VAR_Q.attention import attend_cached
+    from VAR_Q.quant import VAR_Q
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    if name == "attn":        # the step's last scale at a quarter of the batch: 512 CTAs of the tensor-core kernel
+        B, lq, lk = 16, STEPS_L[-1], L_TOTAL
+        kq = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=lk)
+        vq = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=lk)
+        kq.append(torch.nn.functional.normalize(torch.randn((B, lk, HEADS, HEAD_DIM), generator=g, device=dev), dim=-1))
+        vq.append(torch.randn((B, lk, HEADS, HEAD_DIM), generator=g, device=dev).to(torch.bfloat16))
+        q = torch.nn.functional.normalize(torch.randn((B, lq, HEADS, HEAD_DIM), generator=g, device=dev), dim=-1) * Q_GAIN
+        fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
+        nbytes = None
+    else:                     # "quant": 252 MB of fp32 K, per-head INT8, batch-shared groups
+        x = torch.randn((128, 256, 30, 64), generator=g, device=dev)
+        qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=256)
+        fn = lambda: qz.quant(x)
+        nbytes = x.numel() * 5
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    print(json.dumps({"case": name, "ms": ms, "GB/s": None if nbytes is None else nbytes / ms / 1e6}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -391,7 +421,10 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--case", choices=("attn", "quant"), help="run one kernel on a small case and exit (profiling aid)")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args.case)
     if args.impl == "reference":
         run_reference(args)
     else:
