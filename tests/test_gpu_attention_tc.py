@@ -126,3 +126,32 @@ def test_full_size_last_scale_is_linear_in_v_and_permutation_invariant():
     kq2, vq2 = cached(k[:, perm].contiguous(), v[:, perm].contiguous())
     tc2, _ = run("tc", q, kq2, vq2, 1.0)
     check(tc2, tc, "token permutation")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("q_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kkw,vkw", [
+    (dict(mode="G_SCALE_HEAD_DIM"), dict(mode="G_SCALE_HEAD_DIM")),
+    (dict(mode="G_SCALE_HEAD_DIM", symmetric=False), dict(mode="G_TOKEN_HEAD", symmetric=False)),
+    (dict(mode="G_TOKEN_HEAD", symmetric=False, group_size=32), dict(mode="G_TOKEN_HEAD", symmetric=False, group_size=32)),
+    (dict(mode="G_TOKEN_HEAD", group_size=16, reduce_batch=False), dict(mode="G_HEAD_DIM")),
+])
+@pytest.mark.parametrize("kb,vb", [(8, 8), (4, 2)])
+def test_groupings_whose_k_scale_varies_along_head_dim(D, q_dtype, kkw, vkw, kb, vb):
+    """Per-dim and group-wise K: the kernel dequantises K into hi + lo fp16 tiles (two MMAs)."""
+    fmt, B, H = "BLHc", 2, 3
+    steps = (1, 4, 9, 16, 25, 36, 64, 100, 169)
+    kkw, vkw = dict(kkw), dict(vkw)
+    km, vm = kkw.pop("mode"), vkw.pop("mode")
+    kq, vq = VAR_Q(kb, fmt, km, **kkw), VAR_Q(vb, fmt, vm, **vkw)
+    kr, vr = O.OracleVARQ(kb, fmt, km, **kkw), O.OracleVARQ(vb, fmt, vm, **vkw)
+    for si, n in enumerate(steps):
+        k = O.synthetic_kv((B, n, H, D), fmt, 300 + si, n_outlier=4)
+        v = O.synthetic_kv((B, n, H, D), fmt, 400 + si, n_outlier=0)
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    q = torch.randn((B, 169, H, D), generator=torch.Generator().manual_seed(D + kb)).to(q_dtype)
+    scale = 1.0 / D ** 0.5
+    out, launches = run("tc", q.to(DEV), kq, vq, scale)
+    assert launches == 1
+    check(out, O.attention(q, kd, vd, fmt, scale), f"D={D} {q_dtype} K{kkw} V{vkw} {kb}/{vb}")

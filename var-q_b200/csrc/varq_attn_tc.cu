@@ -143,17 +143,19 @@ __device__ __forceinline__ uint32_t tile_off(int row, int col, int rows) {
 }
 
 // ---------------------------------------------------------------- shared-memory plan
-template <int D, int NQ> struct TcPlan {
+template <int D, int NQ, bool KS> struct TcPlan {
     static constexpr int N = (D == 64) ? 128 : 64;           // keys per tile
     static constexpr int Q_BYTES = TC_M * D * 2;              // one fp16 Q tile
     static constexpr int KV_BYTES = N * D * 2;                // one fp16 K (or V) tile
     static constexpr int P_BYTES = TC_M * N * 2;
     static constexpr int PK_BYTES = N * D;                    // packed staging at 8 bits (largest)
+    static constexpr int KT = KS ? 2 : 1;                     // K operand tiles per stage (hi, lo when K is dequantised)
+    static constexpr int PST = KS ? 1 : 2;                    // P buffers
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_K = OFF_Q + NQ * Q_BYTES;        // [2]
-    static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;        // [2]
-    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [2]
-    static constexpr int OFF_PK = OFF_P + 2 * P_BYTES;        // [2][K, V]
+    static constexpr int OFF_K = OFF_Q + NQ * Q_BYTES;        // [2][KT]
+    static constexpr int OFF_V = OFF_K + 2 * KT * KV_BYTES;   // [2]
+    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [PST]
+    static constexpr int OFF_PK = OFF_P + PST * P_BYTES;      // [2][K, V]
     static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
     static constexpr int OFF_BAR = OFF_KS + 4 * 6 * N * 4;    // mbarriers
     static constexpr int N_BARS = 19;
@@ -243,44 +245,99 @@ __device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* 
 
 // Convert `BITS`-wide codes of one packed word to fp16 and write them to the operand tile.
 // EXACT: raw integer codes; otherwise (code - z) * s.
-template <int BITS, bool EXACT>
-__device__ __forceinline__ void put_word(unsigned char* tile, int key, int w, uint32_t word, int rows, float s, float z) {
-    constexpr int VPW = 32 / BITS;
-    __half h[VPW];
-#pragma unroll
-    for (int j = 0; j < VPW; ++j) {
-        const float c = (float)field<BITS>(word, j);
-        h[j] = __float2half_rn(EXACT ? c : (c - z) * s);
-    }
-    const int d0 = w * VPW;
-    if constexpr (VPW == 4) {
-        *reinterpret_cast<uint2*>(tile + tile_off(key, d0, rows)) = *reinterpret_cast<uint2*>(h);
-    } else {
-#pragma unroll
-        for (int c8 = 0; c8 < VPW / 8; ++c8)
-            *reinterpret_cast<uint4*>(tile + tile_off(key, d0 + 8 * c8, rows)) = *reinterpret_cast<uint4*>(h + 8 * c8);
-    }
-}
-
-template <int BITS, bool EXACT>
+// General V path: (code - zp) * scale in fp32, rounded to fp16, for groupings whose scale varies along
+// head_dim (per-dim, group-wise); parameters are fetched per word, or per element when a word spans groups.
+template <int BITS>
 __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
                                              int ptid, const ParamView& pv, int b, int h, int k0, int nthr = 128) {
     constexpr int VPW = 32 / BITS;
     const int total = min(N, (n_valid + 31) & ~31) * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
+    const bool uniform = (pv.group % VPW) == 0;
     for (int idx = ptid; idx < total; idx += nthr) {
         const int key = idx >> wshift, w = idx & (W - 1);
-        uint32_t word = 0;
-        float s = 0.f, z = 0.f;
+        __half hv[VPW];
         if (key < n_valid) {
-            word = packed[idx];
-            if constexpr (!EXACT) {
-                const long long pi = pv.index(b, pv.row(k0 + key), h, w * VPW);
+            const uint32_t word = packed[idx];
+            const int row = pv.row(k0 + key);
+            float s = 0.f, z = 0.f;
+            if (uniform) {
+                const long long pi = pv.index(b, row, h, w * VPW);
                 s = __ldg(pv.scale + pi);
                 z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
             }
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (!uniform) {
+                    const long long pi = pv.index(b, row, h, w * VPW + j);
+                    s = __ldg(pv.scale + pi);
+                    z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+                }
+                hv[j] = __float2half_rn(((float)field<BITS>(word, j) - z) * s);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) hv[j] = __float2half_rn(0.f);
         }
-        put_word<BITS, EXACT>(tile, key, w, word, N, s, z);
+        const int d0 = w * VPW;
+        if constexpr (VPW == 4) {
+            *reinterpret_cast<uint2*>(tile + tile_off(key, d0, N)) = *reinterpret_cast<uint2*>(hv);
+        } else {
+#pragma unroll
+            for (int c8 = 0; c8 < VPW / 8; ++c8)
+                *reinterpret_cast<uint4*>(tile + tile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hv + 8 * c8);
+        }
+    }
+}
+
+// K dequantised to fp32 and split into two fp16 operand tiles, hi = fp16(k) and lo = fp16(k - hi):
+// Q (hi + lo) reproduces k to 2^-22, so groupings whose K scale varies along head_dim (per-dim,
+// group-wise) keep an essentially exact QK^T at the price of a second MMA.
+template <int BITS>
+__device__ __forceinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
+                                                   int n_valid, int N, int W, int ptid, const ParamView& pv, int b, int h, int k0) {
+    constexpr int VPW = 32 / BITS;
+    const int total = N * W;
+    const int wshift = __ffs(W) - 1;
+    const bool uniform = (pv.group % VPW) == 0;
+    for (int idx = ptid; idx < total; idx += 128) {
+        const int key = idx >> wshift, w = idx & (W - 1);
+        __half hh[VPW], hl[VPW];
+        if (key < n_valid) {
+            const uint32_t word = packed[idx];
+            const int row = pv.row(k0 + key);
+            float s = 0.f, z = 0.f;
+            if (uniform) {
+                const long long pi = pv.index(b, row, h, w * VPW);
+                s = __ldg(pv.scale + pi);
+                z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (!uniform) {
+                    const long long pi = pv.index(b, row, h, w * VPW + j);
+                    s = __ldg(pv.scale + pi);
+                    z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+                }
+                const float k = ((float)field<BITS>(word, j) - z) * s;
+                hh[j] = __float2half_rn(k);
+                hl[j] = __float2half_rn(k - __half2float(hh[j]));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) { hh[j] = __float2half_rn(0.f); hl[j] = hh[j]; }
+        }
+        const int d0 = w * VPW;
+        if constexpr (VPW == 4) {
+            *reinterpret_cast<uint2*>(tile_hi + tile_off(key, d0, N)) = *reinterpret_cast<uint2*>(hh);
+            *reinterpret_cast<uint2*>(tile_lo + tile_off(key, d0, N)) = *reinterpret_cast<uint2*>(hl);
+        } else {
+#pragma unroll
+            for (int c8 = 0; c8 < VPW / 8; ++c8) {
+                *reinterpret_cast<uint4*>(tile_hi + tile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hh + 8 * c8);
+                *reinterpret_cast<uint4*>(tile_lo + tile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hl + 8 * c8);
+            }
+        }
     }
 }
 
@@ -349,9 +406,9 @@ __device__ __forceinline__ void softmax_exp32(const uint32_t (&raw)[32], uint32_
     corr += c0s + c1s;
 }
 
-template <int D, int NQ>
+template <int D, int NQ, bool KS>
 __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int kb, int vb) {
-    using P = TcPlan<D, NQ>;
+    using P = TcPlan<D, NQ, KS>;
     constexpr int N = P::N;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
@@ -419,7 +476,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         // ---- Q tile -> shared (fp16 hi [, lo]) by the softmax and MMA warps; the producers are already at work
         constexpr int CH = D / 8;   // 16-byte chunks per row
         const int qtid = warp < 8 ? tid : 256 + lane;
-        const bool want_qsum = a.kp.zp != nullptr;
+        const bool want_qsum = !KS && a.kp.zp != nullptr;
         for (int i = qtid; i < TC_M * CH; i += 288) {
             const int r = i / CH, c = i - r * CH;
             float v[8];
@@ -463,7 +520,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         };
         const bool v_exact = a.vp.group == D;               // V scale constant along head_dim: folded into P
         const bool v_zp = v_exact && a.vp.zp != nullptr;
-        const bool k_zp = a.kp.zp != nullptr;
+        const bool k_zp = !KS && a.kp.zp != nullptr;      // a dequantised K already carries its zero-point
         const float qsum = k_zp ? s_qsum[r] : 0.f;
         float m_used = -FLT_MAX, l_run = 0.f, corr = 0.f;
         bool ok = true;
@@ -529,14 +586,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
             l_run *= alpha;
             corr *= alpha;
-            if (ok && j >= 2) {   // the P buffer is free once the MMA that read it has completed
-                ok = mbar_wait(&bar_pv[buf], ((j - 2) >> 1) & 1, abort_flag, 13);
+            if (ok && j >= P::PST) {   // the P buffer is free once the MMA that read it has completed
+                const int jp = j - P::PST;
+                ok = mbar_wait(&bar_pv[jp & 1], (jp >> 1) & 1, abort_flag, 13);
                 ok = __all_sync(0xffffffffu, ok);
             }
             if (quarter == 0) TC_TRACE(half, j, 3);
             if (ok) {
                 // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
-                unsigned char* prow = smem + P::OFF_P + buf * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+                unsigned char* prow = smem + P::OFF_P + (buf & (P::PST - 1)) * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
                 for (int c0 = 0; c0 < NH; c0 += 32) {
                     const uint32_t(&rw)[32] = *reinterpret_cast<const uint32_t(*)[32]>(raw + c0);
@@ -609,9 +667,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             nsc = 0.f; nzs = 0.f; nvsc = 1.f; nvzp = 0.f;
             const int key = j * N + ptid;
             if (j < T && ptid < N && key < a.Lk) {
-                const long long pi = a.kp.index(b, a.kp.row(key), h, 0);
-                nsc = __ldg(a.kp.scale + pi);
-                if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
+                if constexpr (KS) {
+                    nsc = 1.f;                       // S needs only softmax_scale * log2(e)
+                } else {
+                    const long long pi = a.kp.index(b, a.kp.row(key), h, 0);
+                    nsc = __ldg(a.kp.scale + pi);
+                    if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
+                }
                 if (v_exact) {
                     const long long vi = a.vp.index(b, a.vp.row(key), h, 0);
                     nvsc = __ldg(a.vp.scale + vi);
@@ -632,11 +694,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
             if (warp == 8) TC_TRACE(2, j, 2);
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
-            unsigned char* tk = smem + P::OFF_K + s * P::KV_BYTES;
+            unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
             if (ok) {
-                if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
-                else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
-                else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
+                if constexpr (KS) {
+                    const int k0 = j * N;
+                    if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+                    else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+                    else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+                } else {
+                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
+                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
+                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
+                }
                 if (warp == 8) TC_TRACE(2, j, 3);
                 if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
                     float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 6 * N;
@@ -698,9 +767,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                     else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                 } else {
-                    if (vb == 8) dequant_tile<8, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
-                    else if (vb == 4) dequant_tile<4, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
-                    else dequant_tile<2, false>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_v[s]);
@@ -735,7 +804,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         auto issue_pv = [&](int j) {
             const int s = j & 1;
             const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
-            const uint64_t pd = pd0 + (uint64_t)((s * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
+            const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
 #pragma unroll
             for (int kk = 0; kk < N / 16; ++kk)
                 if (kk < ksteps) tc_mma_f16(tmem_base + P::COL_O, pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
@@ -749,14 +818,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (!ok) break;
             TC_TRACE(3, j, 1);
             tc_fence_after();
-            const uint64_t kd = kd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
+            const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
+            // exact-code K: S = Q_hi K [+ Q_lo K]; dequantised K: S = Q_hi K_hi + Q_hi K_lo [+ Q_lo K_hi]
+            bool first = true;
 #pragma unroll
             for (int qi = 0; qi < NQ; ++qi) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)
-                    tc_mma_f16(tmem_base + P::COL_S + s * N,
-                               qd0 + (uint64_t)((qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
-                               kd + (uint64_t)(((kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S, (qi > 0 || kk > 0) ? 1u : 0u);
+                for (int ki = 0; ki < P::KT; ++ki) {
+                    if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        tc_mma_f16(tmem_base + P::COL_S + s * N,
+                                   qd0 + (uint64_t)((qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                                   kd + (uint64_t)((ki * P::KV_BYTES + (kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S,
+                                   first ? 0u : 1u);
+                        first = false;
+                    }
+                }
             }
             tc_commit(&bar_s[s]);
             TC_TRACE(3, j, 2);
@@ -793,7 +871,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 // ---------------------------------------------------------------- host side
 bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
     if (a.D != 64 && a.D != 128) return false;
-    if (a.kp.group != a.D) return false;                       // K scale must be constant along head_dim
     if ((a.wk & 3) || (a.wv & 3)) return false;                // 16-byte rows for the bulk copies
     if (a.ks_l != a.wk || a.vs_l != a.wv) return false;        // tokens of one (sample, head) contiguous
     if (!a.k16 || !a.v16) return false;
@@ -801,22 +878,22 @@ bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
     return true;
 }
 
-template <int D, int NQ>
+template <int D, int NQ, bool KS>
 static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
-    using P = TcPlan<D, NQ>;
+    using P = TcPlan<D, NQ, KS>;
     static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
     const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
     static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
     int dev = 0;
     VARQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int nqt = (a.Lq + TC_M - 1) / TC_M;
     if ((long long)a.B * a.H > 65535) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: batch x heads > 65535");
     dim3 grid(nqt, a.B * a.H);
-    attn_tc_kernel<D, NQ><<<grid, TC_THREADS, smem, st>>>(a, kb, vb);
+    attn_tc_kernel<D, NQ, KS><<<grid, TC_THREADS, smem, st>>>(a, kb, vb);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     return VARQ_OK;
@@ -824,8 +901,13 @@ static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
 
 int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
     const bool split_q = a.q_dtype == VARQ_F32;    // fp16/bf16 queries are exact in one fp16 term
-    if (a.D == 64) return split_q ? launch_tc<64, 2>(a, kb, vb, st) : launch_tc<64, 1>(a, kb, vb, st);
-    return split_q ? launch_tc<128, 2>(a, kb, vb, st) : launch_tc<128, 1>(a, kb, vb, st);
+    const bool split_k = a.kp.group != a.D;        // K scale varies along head_dim: dequantise K, hi + lo tiles
+    if (a.D == 64) {
+        if (split_k) return split_q ? launch_tc<64, 2, true>(a, kb, vb, st) : launch_tc<64, 1, true>(a, kb, vb, st);
+        return split_q ? launch_tc<64, 2, false>(a, kb, vb, st) : launch_tc<64, 1, false>(a, kb, vb, st);
+    }
+    if (split_k) return split_q ? launch_tc<128, 2, true>(a, kb, vb, st) : launch_tc<128, 1, true>(a, kb, vb, st);
+    return split_q ? launch_tc<128, 2, false>(a, kb, vb, st) : launch_tc<128, 1, false>(a, kb, vb, st);
 }
 
 int attn_tc_status(int* out) {
