@@ -5,4 +5,4 @@ Importable under the module names the VAR and Infinity attention hooks use
 that contains this package is on ``sys.path`` -- the same convention as the
 reference project (VAR/models/basic_var.py:11-21, Infinity/infinity/models/basic.py:24-28).
 """
-__all__ = ["quant", "pack_unpack", "config_loader", "attention", "sharding"]
+__all__ = ["quant", "pack_unpack", "config_loader", "attention", "hooks", "sharding"]
