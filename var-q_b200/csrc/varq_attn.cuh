@@ -83,6 +83,9 @@ __device__ __forceinline__ void store_o_row32(void* o, int dtype, long long off,
 
 size_t attn_small_workspace_bytes(int B, int H, int Lq, int Lk, int D);
 int attn_small_run(AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
+bool attn_stream_eligible(const AttnArgs& a, int kb, int vb);
+size_t attn_stream_workspace_bytes(int B, int H, int Lq, int Lk, int D);
+int attn_stream_run(AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
 bool attn_tc_eligible(const AttnArgs& a, int kb, int vb);
 int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st);
 int attn_tc_status(int* out);

@@ -14,7 +14,8 @@ extern "C" size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, in
                                             int32_t k_store_bits, int32_t v_store_bits) {
     (void)k_store_bits; (void)v_store_bits;
     if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0 || D <= 0) return 0;
-    return attn_small_workspace_bytes(B, H, Lq, Lk, D);
+    const size_t s1 = attn_small_workspace_bytes(B, H, Lq, Lk, D), s2 = attn_stream_workspace_bytes(B, H, Lq, Lk, D);
+    return s1 > s2 ? s1 : s2;
 }
 
 extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_codes, const varq_tensor_t* v_codes,
@@ -53,9 +54,11 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.splits = 1; a.tiles_per_split = 0; a.ws = reinterpret_cast<float*>(workspace);
     // small query counts stay on the CUDA-core kernel (memory-bound); the rest goes to the tensor cores
-    const char* force = getenv("VARQ_ATTN_PATH");       // "small" / "tc": testing aid, not a fallback switch
+    const char* force = getenv("VARQ_ATTN_PATH");       // "small" / "stream" / "tc": testing aid, not a fallback switch
     const bool want_tc = force ? (force[0] == 't') : (Lq > 8);
     if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, (cudaStream_t)stream);
+    const bool want_stream = force ? (force[0] == 's' && force[1] == 't') : (Lq <= 8);
+    if (want_stream && attn_stream_eligible(a, kb, vb)) return attn_stream_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 

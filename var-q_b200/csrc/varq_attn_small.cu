@@ -319,6 +319,14 @@ __global__ void attn_small_merge_kernel(AttnArgs a, int n_qtiles) {
     }
 }
 
+void attn_small_merge_launch(const AttnArgs& a, int n_qtiles, cudaStream_t st) {
+    const long long total = (long long)a.B * a.H * a.Lq * a.D;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    attn_small_merge_kernel<<<(unsigned)blocks, 256, 0, st>>>(a, n_qtiles);
+}
+
 static int pick_splits(int B, int H, int Lq, int Lk, int& tiles_per_split) {
     const int n_tiles = (Lk + A1_TILE - 1) / A1_TILE;
     const long long base = (long long)B * H * ((Lq + A1_QT - 1) / A1_QT);
