@@ -93,12 +93,17 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
 #pragma unroll
     for (int qi = 0; qi < QT; ++qi) {
         float part = 0.f;
+        float lo8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, hi8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (qi < nq) {
+            const long long off = b * a.qs_b + (long long)(q0 + qi) * a.qs_l + h * a.qs_h + d0;
+            load_q8(a.q, a.q_dtype, off, lo8);
+            load_q8(a.q, a.q_dtype, off + 8, hi8);
+        }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float v = 0.f;
-            if (qi < nq) v = load_q_elem(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + qi) * a.qs_l + h * a.qs_h + d0 + j) * a.scale_log2;
-            q[qi][j] = v;
-            part += v;
+        for (int j = 0; j < 8; ++j) {
+            q[qi][j] = lo8[j] * a.scale_log2;
+            q[qi][j + 8] = hi8[j] * a.scale_log2;
+            part += q[qi][j] + q[qi][j + 8];
         }
 #pragma unroll
         for (int m = 1; m < LPK; m <<= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
