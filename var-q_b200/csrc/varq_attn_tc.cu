@@ -32,8 +32,16 @@ constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
         if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && a.ws && (j) < 32)      \
             reinterpret_cast<long long*>(a.ws)[((role) * 32 + (j)) * 8 + (ev)] = clock64();        \
     } while (0)
+#define TC_TRACE_CTA(t0)                                                                                   \
+    do {                                                                                                   \
+        if (threadIdx.x == 0 && a.ws) {                                                                    \
+            const long long id = blockIdx.y * (long long)gridDim.x + blockIdx.x;                           \
+            if (id < 60000) reinterpret_cast<long long*>(a.ws)[4096 + id] = clock64() - (t0);              \
+        }                                                                                                  \
+    } while (0)
 #else
 #define TC_TRACE(role, j, ev) do { } while (0)
+#define TC_TRACE_CTA(t0) do { } while (0)
 #endif
 
 __device__ int g_tc_status = 0;   // first failure code of any launch since the last read (0 = none)
@@ -210,7 +218,7 @@ template <> struct Codes<2> {   // one word -> 16 halves
 
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS>
-__device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
+__device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
                                            int rows = -1) {
     // rows [n_valid, rows) are zero-filled; consumers never read past `rows`
     if (rows < 0) rows = N;
@@ -248,7 +256,7 @@ __device__ __forceinline__ void codes_tile(unsigned char* tile, const uint32_t* 
 // General V path: (code - zp) * scale in fp32, rounded to fp16, for groupings whose scale varies along
 // head_dim (per-dim, group-wise); parameters are fetched per word, or per element when a word spans groups.
 template <int BITS>
-__device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
+__device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
                                              int ptid, const ParamView& pv, int b, int h, int k0, int nthr = 128) {
     constexpr int VPW = 32 / BITS;
     const int total = min(N, (n_valid + 31) & ~31) * W;
@@ -294,7 +302,7 @@ __device__ __forceinline__ void dequant_tile(unsigned char* tile, const uint32_t
 // Q (hi + lo) reproduces k to 2^-22, so groupings whose K scale varies along head_dim (per-dim,
 // group-wise) keep an essentially exact QK^T at the price of a second MMA.
 template <int BITS>
-__device__ __forceinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
+__device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
                                                    int n_valid, int N, int W, int ptid, const ParamView& pv, int b, int h, int k0) {
     constexpr int VPW = 32 / BITS;
     const int total = N * W;
@@ -435,6 +443,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
     const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
     if (warp == 0) TC_TRACE(3, 30, 0);
+    const long long cta_t0 = clock64();
+    (void)cta_t0;
     const int aq = (nq + 31) >> 5;                  // TMEM lane quarters that hold real queries
     float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
 
@@ -538,17 +548,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             const float* vz = ks + 5 * N;
             const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
             // ---- this thread's half row of S, read from TMEM once; pass 1: its maximum
-            uint32_t raw[NH];
+            const bool live = half * NH < min(N, a.Lk - j * N);     // this half of the tile holds at least one key
+            // Both passes walk the half row in 32-column chunks re-read from TMEM; the loops are kept
+            // rolled so that the code the softmax warps execute per tile stays small.
             float m_half = -FLT_MAX;
-            if (ok) {
+            if (ok && live) {
                 tc_fence_after();
-#pragma unroll
-                for (int c0 = 0; c0 < NH; c0 += 32) tmem_ld32(s_addr + c0, *reinterpret_cast<uint32_t(*)[32]>(raw + c0));
-                tmem_wait_ld();
-                if (quarter == 0) TC_TRACE(half, j, 5);
-#pragma unroll
+#pragma unroll 1
                 for (int c0 = 0; c0 < NH; c0 += 32) {
-                    const uint32_t(&rw)[32] = *reinterpret_cast<const uint32_t(*)[32]>(raw + c0);
+                    uint32_t rw[32];
+                    tmem_ld32(s_addr + c0, rw);
+                    tmem_wait_ld();
                     m_half = k_zp ? softmax_max32<true>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half)
                                   : softmax_max32<false>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half);
                 }
@@ -592,12 +602,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 ok = __all_sync(0xffffffffu, ok);
             }
             if (quarter == 0) TC_TRACE(half, j, 3);
-            if (ok) {
+            if (ok && live) {
                 // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
                 unsigned char* prow = smem + P::OFF_P + (buf & (P::PST - 1)) * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
+#pragma unroll 1
                 for (int c0 = 0; c0 < NH; c0 += 32) {
-                    const uint32_t(&rw)[32] = *reinterpret_cast<const uint32_t(*)[32]>(raw + c0);
+                    uint32_t rw[32];
+                    tmem_ld32(s_addr + c0, rw);
+                    tmem_wait_ld();
                     uint32_t ph[16];
                     if (!v_exact) {
                         if (k_zp) softmax_exp32<true, false, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
@@ -616,6 +628,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     for (int q4 = 0; q4 < 4; ++q4)
                         sts128(blk + (((ch0 + q4) ^ (r & 7)) << 4), ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
                 }
+            }
+            if (ok) {
                 fence_async_smem();
                 tc_fence_before();
                 mbar_arrive(&bar_p[buf]);
@@ -702,9 +716,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
                     else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
                 } else {
-                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid);
-                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid);
-                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid);
+                    const int krows = min(N, ((n_valid + N / 2 - 1) / (N / 2)) * (N / 2));   // softmax reads whole halves of a tile
+                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, 128, krows);
+                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, 128, krows);
+                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, 128, krows);
                 }
                 if (warp == 8) TC_TRACE(2, j, 3);
                 if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
@@ -862,6 +877,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     if (warp == 0) TC_TRACE(3, 30, 4);
     __syncthreads();
     if (warp == 0) TC_TRACE(3, 30, 5);
+    TC_TRACE_CTA(cta_t0);
     if (warp == 15) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
