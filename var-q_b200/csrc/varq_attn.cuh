@@ -35,14 +35,16 @@ __device__ __forceinline__ void load_q8(const void* q, int dtype, long long off,
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     } else {
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(addr));
-        if (dtype == VARQ_F16) {
-            const __half* e = reinterpret_cast<const __half*>(&raw);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __half2float(e[j]);
-        } else {
-            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&raw);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(e[j]);
+        for (int j = 0; j < 4; ++j) {
+            if (dtype == VARQ_F16) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                v[2 * j] = f.x; v[2 * j + 1] = f.y;
+            } else {                         // a bf16 is the upper half of an fp32
+                v[2 * j] = __uint_as_float(w[j] << 16);
+                v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+            }
         }
     }
 }
@@ -66,17 +68,18 @@ __device__ __forceinline__ void store_o_row32(void* o, int dtype, long long off,
         uint4* p = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(o) + off);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            uint4 raw;
-            if (dtype == VARQ_F16) {
-                __half* e = reinterpret_cast<__half*>(&raw);
+            uint32_t w[4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) e[j] = __float2half_rn(v[8 * c + j]);
-            } else {
-                __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&raw);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16_rn(v[8 * c + j]);
+            for (int j = 0; j < 4; ++j) {
+                if (dtype == VARQ_F16) {
+                    const __half2 h = __floats2half2_rn(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]);
+                    w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]);
+                    w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
             }
-            p[c] = raw;
+            p[c] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
 }

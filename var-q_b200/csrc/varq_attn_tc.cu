@@ -1,18 +1,25 @@
 // Attention over the packed cache on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
 // One CTA = one (sample, head) x 128 queries, looping over key tiles.  Thirteen warps:
-//   warps 0-7  softmax: two threads share query row r (TMEM lane r), each taking half of the
-//              tile's keys; they read S from TMEM, apply the per-key scale / zero-point of K,
-//              do the online softmax with lazy rescaling of O, write P (fp16) to shared memory,
-//              and at the end normalise and store;
+//   warps 0-7  softmax: two threads share query row r (TMEM lane r), each owning half of every
+//              tile's keys AND its own output accumulator, so the pair never has to agree on a
+//              running maximum: a thread reads its S columns from TMEM 32 at a time, applies the
+//              per-key scale / zero-point of K, exponentiates against its own lazily updated
+//              reference maximum and writes P (fp16) to shared memory.  The two partial results
+//              of a row are merged once, in the epilogue;
 //   warps 8-11 (K) and 12-14 (V) producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
 //              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
-//              K as exact fp16 integer codes, V as fp16 (code - zp) * scale;
-//   warp  15   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
-//              O += P V, and commits completion to mbarriers.
+//              K as exact fp16 integer codes, V as fp16 (code - zp) * scale; the K producers also
+//              write the per-key tables and a small operand tile holding 1 / V-scale and the V
+//              zero-point of each key (fp16 hi + lo pairs);
+//   warp  15   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM),
+//              O_half += P V and, with the small tile as B operand, the softmax normaliser
+//              and zero-point correction sum_k P (the tensor core adds up exactly the rounded P
+//              that it multiplies with V), and commits completion to mbarriers.
 // Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
 // no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
-// rounded to fp16 (bf16 would miss the 1e-3 relative-L2 target by 10x).
+// rounded to fp16 (bf16 would miss the 1e-3 relative-L2 target by 10x).  A V scale below 2^-20
+// is folded as 2^-20 (the error is below 127 * 2^-20 per unit of attention weight).
 // Every wait is bounded: on expiry the kernel records a status code and all roles drain out.
 #include <cfloat>
 
@@ -26,10 +33,10 @@ constexpr int TC_M = 128;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
 
 #ifdef VARQ_TC_TRACE
-// development aid: cycle stamps of CTA (0,0), [role][tile][event], written to the workspace pointer
+// development aid: cycle stamps of the last CTA of row 0, [role][tile][event], written to the workspace pointer
 #define TC_TRACE(role, j, ev)                                                                      \
     do {                                                                                           \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && a.ws && (j) < 32)      \
+        if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && a.ws && (j) < 32)      \
             reinterpret_cast<long long*>(a.ws)[((role) * 32 + (j)) * 8 + (ev)] = clock64();        \
     } while (0)
 #define TC_TRACE_CTA(t0)                                                                                   \
@@ -68,15 +75,21 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the limit expires or another thread has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (i > 32) __nanosleep(40);
+// The loop is inline: a call costs a few hundred cycles of register save / restore around it and
+// puts stack traffic on the critical path of whoever waits.  Only the give-up branch is out of line.
+__device__ __noinline__ bool mbar_give_up(volatile int* abort_flag, int code, uint32_t tries) {
+    if (tries >= TC_SPIN_LIMIT) {
+        *abort_flag = 1;
+        atomicCAS(&g_tc_status, 0, code);
     }
-    *abort_flag = 1;
-    atomicCAS(&g_tc_status, 0, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+    uint32_t tries = 0;
+    while (!mbar_try(bar, parity)) {     // a failed try_wait has already been suspended by the hardware for a while
+        if (++tries >= TC_SPIN_LIMIT || *abort_flag) return mbar_give_up(abort_flag, code, tries);
+    }
+    return true;
 }
 __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -113,6 +126,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -164,15 +190,21 @@ template <int D, int NQ, bool KS> struct TcPlan {
     static constexpr int OFF_V = OFF_K + 2 * KT * KV_BYTES;   // [2]
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [PST]
     static constexpr int OFF_PK = OFF_P + PST * P_BYTES;      // [2][K, V]
-    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][6][N]: K scale, mask bias, mask bias + log2(V scale), K zp*scale, 1/V scale, V zp
-    static constexpr int OFF_BAR = OFF_KS + 4 * 6 * N * 4;    // mbarriers
+    static constexpr int AUX_BYTES = (N / 64) * 16 * 128;     // 16 x N fp16, K-major: rows 0-3 = 1/V-scale hi, lo, V zero-point hi, lo
+    static constexpr int OFF_AUX = OFF_PK + 4 * PK_BYTES;     // [4]
+    static constexpr int OFF_KS = OFF_AUX + 4 * AUX_BYTES;    // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
+    static constexpr int OFF_BAR = OFF_KS + 4 * 3 * N * 4;    // mbarriers
     static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
-    static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][2][2][128]: row halves exchange (parity, slot, half, row)
-    static constexpr int OFF_QSUM = OFF_XCH + 2 * 2 * 2 * 128 * 4;   // float [128]: row sums of Q (zero-point term of K)
+    static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][128]: the two halves of a row exchange their reference maxima
+    static constexpr int OFF_QSUM = OFF_XCH + 2 * 128 * 4;    // float [128]: row sums of Q (zero-point term of K)
     static constexpr int TOTAL = OFF_QSUM + 128 * 4;
-    static constexpr int TMEM_COLS = (2 * N + D) <= 256 ? 256 : 512;
+    // TMEM columns: S double-buffered, then one accumulator per half of the keys:
+    // D output columns followed by 16 columns of sum_k P * (small tile)
+    static constexpr int ACC_COLS = D + 32;
+    static constexpr int TMEM_COLS = 512;
     static constexpr int COL_S = 0, COL_O = 2 * N;
+    static_assert(COL_O + 2 * ACC_COLS <= 512, "TMEM plan exceeds 512 columns");
 };
 
 
@@ -227,7 +259,7 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
     const int ipr = W >> 2;                   // 16-byte items per key row
     const int ishift = __ffs(ipr) - 1;
     const int items = rows * ipr;
-#pragma unroll 2
+#pragma unroll 1
     for (int it = ptid; it < items; it += nthr) {
         const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
         uint4 pk = make_uint4(0u, 0u, 0u, 0u);
@@ -257,7 +289,7 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
 // head_dim (per-dim, group-wise); parameters are fetched per word, or per element when a word spans groups.
 template <int BITS>
 __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
-                                             int ptid, const ParamView& pv, int b, int h, int k0, int nthr = 128) {
+                                             int ptid, const ParamView pv, int b, int h, int k0, int nthr = 128) {
     constexpr int VPW = 32 / BITS;
     const int total = min(N, (n_valid + 31) & ~31) * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
@@ -303,7 +335,7 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
 // group-wise) keep an essentially exact QK^T at the price of a second MMA.
 template <int BITS>
 __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
-                                                   int n_valid, int N, int W, int ptid, const ParamView& pv, int b, int h, int k0) {
+                                                   int n_valid, int N, int W, int ptid, const ParamView pv, int b, int h, int k0) {
     constexpr int VPW = 32 / BITS;
     const int total = N * W;
     const int wshift = __ffs(W) - 1;
@@ -350,68 +382,90 @@ __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned
 }
 
 // ---- softmax over 32 columns of S held in registers.  Per-key tables (shared memory):
-// ks = K scale * softmax_scale * log2(e) (0 past the end), b1 = 0 / -1e30 mask bias,
-// b2 = b1 + log2(V scale), kzs = K zero-point * ks, vinv = 1 / V scale, vz = V zero-point.
+// ks = K scale * softmax_scale * log2(e) (0 past the end), b2 = log2(folded V scale) (-1e30 past the
+// end), kzs = K zero-point * ks.
 // four consecutive table entries with one 16-byte shared-memory load (tables are 16-byte aligned)
 __device__ __forceinline__ float4 tab4(const float* p, int c) { return *reinterpret_cast<const float4*>(p + c); }
 
+constexpr float TC_VS_MIN = 9.5367431640625e-07f;     // 2^-20: smallest V scale folded into P as is
+constexpr float TC_AUX_DOWN = 0.015625f;              // 2^-6 on 1 / V-scale so that it stays inside fp16's range
+constexpr float TC_AUX_UP = 64.f;
+constexpr float TC_ZP_DOWN = 0.00390625f;             // 2^-8 on the V zero-point
+constexpr float TC_ZP_UP = 256.f;
+
+// raw scores -> x = s * ks + b2 [- kzs * qsum] in place (log2 domain, V scale folded in); returns their maximum
 template <bool KZ>
-__device__ __forceinline__ float softmax_max32(const uint32_t (&raw)[32], const float* ks, const float* b1,
-                                               const float* kzs, float qsum, float m) {
-#pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-        const float4 s4 = tab4(ks, c), b4 = tab4(b1, c);
-        float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (KZ) z4 = tab4(kzs, c);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float v = fmaf(__uint_as_float(raw[c + i]), pick(s4, i), pick(b4, i));
-            if (KZ) v = fmaf(-pick(z4, i), qsum, v);
-            m = fmaxf(m, v);
-        }
-    }
-    return m;
-}
-template <bool KZ, bool VX, bool VZ>
-__device__ __forceinline__ void softmax_exp32(const uint32_t (&raw)[32], uint32_t (&ph)[16], const float* ks,
-                                              const float* b2, const float* kzs, const float* vinv, const float* vz,
-                                              float qsum, float m_used, float& l_run, float& corr) {
-    float l0 = 0.f, l1 = 0.f, c0s = 0.f, c1s = 0.f;        // two accumulators shorten the dependent chains
+__device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* ks, const float* b2, const float* kzs, float qsum) {
+    float m0 = -FLT_MAX, m1 = -FLT_MAX;
 #pragma unroll
     for (int c = 0; c < 32; c += 4) {
         const float4 s4 = tab4(ks, c), b4 = tab4(b2, c);
-        float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f), i4 = z4, w4 = z4;
+        float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (KZ) z4 = tab4(kzs, c);
-        if (VX) i4 = tab4(vinv, c);
-        if (VZ) w4 = tab4(vz, c);
+        float x[4];
 #pragma unroll
-        for (int i = 0; i < 4; i += 2) {
-            float x0 = fmaf(__uint_as_float(raw[c + i]), pick(s4, i), pick(b4, i));
-            float x1 = fmaf(__uint_as_float(raw[c + i + 1]), pick(s4, i + 1), pick(b4, i + 1));
-            if (KZ) { x0 = fmaf(-pick(z4, i), qsum, x0); x1 = fmaf(-pick(z4, i + 1), qsum, x1); }
-#if defined(VARQ_ABL_NOEX2)
-            const __half2 h2 = __floats2half2_rn(x0 - m_used, x1 - m_used);
-#else
-            const __half2 h2 = __floats2half2_rn(ex2(x0 - m_used), ex2(x1 - m_used));
-#endif
-#if defined(VARQ_ABL_NOCVT)
-            const float2 pf = make_float2(x0, x1);
-#else
-            const float2 pf = __half22float2(h2);           // the rounded values feed the normaliser too
-#endif
-            if (VX) {
-                l0 = fmaf(pf.x, pick(i4, i), l0);
-                l1 = fmaf(pf.y, pick(i4, i + 1), l1);
-                if (VZ) { c0s = fmaf(pf.x, pick(w4, i), c0s); c1s = fmaf(pf.y, pick(w4, i + 1), c1s); }
-            } else {
-                l0 += pf.x;
-                l1 += pf.y;
-            }
-            ph[(c + i) >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+        for (int i = 0; i < 4; ++i) {
+            x[i] = fmaf(__uint_as_float(rw[c + i]), pick(s4, i), pick(b4, i));
+            if (KZ) x[i] = fmaf(-pick(z4, i), qsum, x[i]);
+            rw[c + i] = __float_as_uint(x[i]);
         }
+        m0 = fmaxf(m0, fmaxf(x[0], x[1]));
+        m1 = fmaxf(m1, fmaxf(x[2], x[3]));
     }
-    l_run += l0 + l1;
-    corr += c0s + c1s;
+    return fmaxf(m0, m1);
+}
+// x -> P = exp2(x - m) rounded to fp16, packed in pairs
+__device__ __forceinline__ void chunk_exp(const uint32_t (&x)[32], float m, uint32_t (&ph)[16]) {
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+        const __half2 h2 = __floats2half2_rn(ex2(__uint_as_float(x[c]) - m), ex2(__uint_as_float(x[c + 1]) - m));
+        ph[c >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+}
+
+// Out-of-line slow path of the softmax warps: the maximum of this thread's scores over the whole tile
+// becomes the reference of the rows that need one, and the accumulator (D output columns + 16 columns of
+// normaliser sums) is multiplied by 2^(old - new).  `pv_done` = barrier of the previous tile's O += P V
+// (nullptr at the first tile, whose MMA overwrites the accumulator).  Returns the row's reference, NaN if a wait expired.
+template <int D, int N>
+__device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const float* ks, const float* b2, const float* kzs, bool k_zp,
+                                            float qsum, float m_used, uint32_t acc, uint64_t* pv_done, uint32_t pv_parity,
+                                            volatile int* abort_flag) {
+    uint32_t rw[32];
+    float tm = -FLT_MAX;
+#pragma unroll 1
+    for (int c = 0; c < nch; ++c) {
+        tmem_ld32(s_addr + c * 32, rw);
+        tmem_wait_ld();
+        tm = fmaxf(tm, k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
+                            : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum));
+    }
+    float alpha = 1.f;
+    if (tm > m_used + 8.f) {
+        alpha = ex2(m_used - tm);       // 0 for a row without a reference yet
+        m_used = tm;
+    }
+    if (pv_done == nullptr) return m_used;
+    bool ok = mbar_wait(pv_done, pv_parity, abort_flag, 12);   // the accumulator is stable
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) return __int_as_float(0x7fc00000);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c0 = 0; c0 < D; c0 += 32) {
+        tmem_ld32(acc + c0, rw);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) rw[i] = __float_as_uint(__uint_as_float(rw[i]) * alpha);
+        tmem_st32(acc + c0, rw);
+    }
+    uint32_t ax[16];
+    tmem_ld16(acc + D, ax);
+    tmem_wait_ld();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) ax[i] = __float_as_uint(__uint_as_float(ax[i]) * alpha);
+    tmem_st16(acc + D, ax);
+    tmem_wait_st();
+    return m_used;
 }
 
 template <int D, int NQ, bool KS>
@@ -493,17 +547,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
             if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v);
-            __half hi[8], lo[8];
+            uint32_t hi[4], lo[4];
             float part = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                hi[j] = __float2half_rn(v[j]);
-                lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
-                part += v[j];
+            for (int j = 0; j < 4; ++j) {
+                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                const float2 hf = __half22float2(h);
+                const __half2 l = __floats2half2_rn(v[2 * j] - hf.x, v[2 * j + 1] - hf.y);
+                hi[j] = *reinterpret_cast<const uint32_t*>(&h);
+                lo[j] = *reinterpret_cast<const uint32_t*>(&l);
+                part += v[2 * j] + v[2 * j + 1];
             }
             const uint32_t off = tile_off(r, c * 8, TC_M);
-            *reinterpret_cast<uint4*>(smem + P::OFF_Q + off) = *reinterpret_cast<uint4*>(hi);
-            if constexpr (NQ == 2) *reinterpret_cast<uint4*>(smem + P::OFF_Q + P::Q_BYTES + off) = *reinterpret_cast<uint4*>(lo);
+            sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
+            if constexpr (NQ == 2) sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
             if (want_qsum && r < nq) atomicAdd(&s_qsum[r], part);
         }
         fence_async_smem();
@@ -520,6 +577,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const int quarter = warp & 3, half = warp >> 2;
         const int r = quarter * 32 + lane;                  // query row = TMEM lane
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t acc = lane_base + P::COL_O + half * P::ACC_COLS;     // this thread's accumulator: D + 16 columns
         float* xch = reinterpret_cast<float*>(smem + P::OFF_XCH);
         // the two warps that share a TMEM lane quarter agree on `ok` and meet at a named barrier
         auto pair_sync_and = [&](bool flag) -> bool {
@@ -528,136 +586,115 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                          : "=r"(all_ok) : "r"((uint32_t)flag), "r"(3 + quarter) : "memory");
             return all_ok != 0;
         };
-        const bool v_exact = a.vp.group == D;               // V scale constant along head_dim: folded into P
-        const bool v_zp = v_exact && a.vp.zp != nullptr;
         const bool k_zp = !KS && a.kp.zp != nullptr;      // a dequantised K already carries its zero-point
         const float qsum = k_zp ? s_qsum[r] : 0.f;
-        float m_used = -FLT_MAX, l_run = 0.f, corr = 0.f;
+        float m_used = -FLT_MAX;                            // reference maximum of this thread's keys (log2 domain)
         bool ok = true;
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
+            if (quarter == 0) TC_TRACE(half, j, 5);
             ok = ok && mbar_wait(&bar_t[j & 3], (j >> 2) & 1, abort_flag, 10);   // per-key tables are visible
             ok = ok && mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
-            if (quarter == 0) TC_TRACE(half, j, 0);
-            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & 3) * 6 * N + half * NH;
-            const float* b1 = ks + N;
-            const float* b2 = ks + 2 * N;
-            const float* kzs = ks + 3 * N;
-            const float* vinv = ks + 4 * N;
-            const float* vz = ks + 5 * N;
-            const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
-            // ---- this thread's half row of S, read from TMEM once; pass 1: its maximum
-            const bool live = half * NH < min(N, a.Lk - j * N);     // this half of the tile holds at least one key
-            // Both passes walk the half row in 32-column chunks re-read from TMEM; the loops are kept
-            // rolled so that the code the softmax warps execute per tile stays small.
-            float m_half = -FLT_MAX;
-            if (ok && live) {
-                tc_fence_after();
-#pragma unroll 1
-                for (int c0 = 0; c0 < NH; c0 += 32) {
-                    uint32_t rw[32];
-                    tmem_ld32(s_addr + c0, rw);
-                    tmem_wait_ld();
-                    m_half = k_zp ? softmax_max32<true>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half)
-                                  : softmax_max32<false>(rw, ks + c0, b1 + c0, kzs + c0, qsum, m_half);
-                }
-            }
-            if (quarter == 0) TC_TRACE(half, j, 1);
-            float* slot = xch + (j & 1) * 512;              // [slot 0][half][row]
-            slot[half * 128 + r] = m_half;
-            ok = pair_sync_and(ok);
             if (!ok) break;
-            if (quarter == 0) TC_TRACE(half, j, 2);
-            const float m_tile = fmaxf(m_half, slot[(half ^ 1) * 128 + r]);
-            // lazy rescale: keep the running reference max until it is exceeded by more than 8 (log2 units)
-            float alpha = 1.f;
-            const bool need = m_tile > m_used + 8.f || j == 0;
-            if (need) {
-                alpha = (j == 0) ? 0.f : ex2(m_used - m_tile);
-                m_used = m_tile;
-            }
-            if (__any_sync(0xffffffffu, need) && j > 0) {
-                ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 12);   // O is stable
-                ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
-                    tc_fence_after();
-#pragma unroll 1
-                    for (int c0 = 0; c0 < DH; c0 += 32) {
-                        uint32_t raw[32];
-                        tmem_ld32(lane_base + P::COL_O + half * DH + c0, raw);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) raw[c] = __float_as_uint(__uint_as_float(raw[c]) * alpha);
-                        tmem_st32(lane_base + P::COL_O + half * DH + c0, raw);
-                    }
-                    tmem_wait_st();
-                }
-            }
-            l_run *= alpha;
-            corr *= alpha;
-            if (ok && j >= P::PST) {   // the P buffer is free once the MMA that read it has completed
+            if (quarter == 0) TC_TRACE(half, j, 0);
+            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & 3) * 3 * N + half * NH;
+            const float* b2 = ks + N;
+            const float* kzs = ks + 2 * N;
+            const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
+            // 32-key chunks of this half that hold at least one key
+            const int nch = min(NH / 32, max(0, (min(N, a.Lk - j * N) - half * NH + 31) >> 5));
+            if (nch > 0 && j >= P::PST) {   // the P buffer is free once the MMA that read it has completed
                 const int jp = j - P::PST;
                 ok = mbar_wait(&bar_pv[jp & 1], (jp >> 1) & 1, abort_flag, 13);
                 ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
             }
-            if (quarter == 0) TC_TRACE(half, j, 3);
-            if (ok && live) {
-                // ---- pass 2: P = exp2(x - m) (times the V scale), rounded to fp16, into the operand tile
+            if (quarter == 0) TC_TRACE(half, j, 1);
+            if (nch > 0) {
+                tc_fence_after();
                 unsigned char* prow = smem + P::OFF_P + (buf & (P::PST - 1)) * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+                int c = 0;
 #pragma unroll 1
-                for (int c0 = 0; c0 < NH; c0 += 32) {
+                while (c < nch) {
                     uint32_t rw[32];
-                    tmem_ld32(s_addr + c0, rw);
+                    tmem_ld32(s_addr + c * 32, rw);
                     tmem_wait_ld();
-                    uint32_t ph[16];
-                    if (!v_exact) {
-                        if (k_zp) softmax_exp32<true, false, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                        else      softmax_exp32<false, false, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                    } else if (v_zp) {
-                        if (k_zp) softmax_exp32<true, true, true>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                        else      softmax_exp32<false, true, true>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                    } else {
-                        if (k_zp) softmax_exp32<true, true, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
-                        else      softmax_exp32<false, true, false>(rw, ph, ks + c0, b2 + c0, kzs + c0, vinv + c0, vz + c0, qsum, m_used, l_run, corr);
+                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 6);
+                    const float cm = k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
+                                          : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum);
+                    if (__any_sync(0xffffffffu, cm > m_used + 8.f)) {
+                        // Rare: some row of this warp meets a score more than 2^8 above its reference.  A new
+                        // reference is taken, the accumulator rescaled, and the tile's chunks are redone
+                        // (P of earlier chunks was written against the old reference).
+                        m_used = new_reference<D, N>(s_addr, nch, ks, b2, kzs, k_zp, qsum, m_used, acc,
+                                                     j > 0 ? &bar_pv[(j - 1) & 1] : nullptr, ((j - 1) >> 1) & 1, abort_flag);
+                        ok = __all_sync(0xffffffffu, m_used == m_used);
+                        if (!ok) break;
+                        c = 0;
+                        continue;
                     }
-                    const int col = half * NH + c0;         // key index of the chunk inside the tile
+                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 7);
+                    uint32_t ph[16];
+                    chunk_exp(rw, m_used, ph);
+                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 2);
+                    const int col = half * NH + c * 32;     // key index of the chunk inside the tile
                     unsigned char* blk = prow + (col >> 6) * (TC_M * 128);
                     const int ch0 = (col & 63) >> 3;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
                         sts128(blk + (((ch0 + q4) ^ (r & 7)) << 4), ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
+                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 3);
+                    ++c;
                 }
+                if (!ok) break;
             }
-            if (ok) {
-                fence_async_smem();
-                tc_fence_before();
-                mbar_arrive(&bar_p[buf]);
-                if (quarter == 0) TC_TRACE(half, j, 4);
-            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(&bar_p[buf]);
+            if (quarter == 0) TC_TRACE(half, j, 4);
         }
-        // ---- the two halves of a row add up their normalisers, then each stores half of the columns
-        float* fin = xch + 256;                             // [parity][slot 1][half][row]: free of max traffic
-        fin[half * 128 + r] = l_run;
-        fin[512 + half * 128 + r] = corr;
+        // ---- merge the two halves of a row: o = sum_h w_h (O_h - corr_h) / sum_h w_h L_h, w_h = 2^(m_h - m)
+        xch[half * 128 + r] = m_used;
         ok = ok && mbar_wait(bar_o, 0, abort_flag, 14);
         if (warp == 0) TC_TRACE(3, 30, 3);
         ok = __all_sync(0xffffffffu, ok);
         ok = pair_sync_and(ok);
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / (l_run + fin[(half ^ 1) * 128 + r]);
-            const float corr_row = corr + fin[512 + (half ^ 1) * 128 + r];
+            const bool two = a.Lk > NH;                     // the second half of the keys ever held a key
+            const float m_a = half == 0 ? m_used : xch[r], m_b = two ? (half == 1 ? m_used : xch[128 + r]) : -FLT_MAX;
+            const float m = fmaxf(m_a, m_b);
+            const float w_a = ex2(m_a - m), w_b = two ? ex2(m_b - m) : 0.f;
+            const uint32_t acc_a = lane_base + P::COL_O, acc_b = acc_a + P::ACC_COLS;
+            uint32_t ax[16];
+            tmem_ld16(acc_a + D, ax);
+            tmem_wait_ld();
+            float den = w_a * (__uint_as_float(ax[0]) + __uint_as_float(ax[1]));
+            float cz = w_a * (__uint_as_float(ax[2]) + __uint_as_float(ax[3]));
+            if (two) {
+                tmem_ld16(acc_b + D, ax);
+                tmem_wait_ld();
+                den = fmaf(w_b, __uint_as_float(ax[0]) + __uint_as_float(ax[1]), den);
+                cz = fmaf(w_b, __uint_as_float(ax[2]) + __uint_as_float(ax[3]), cz);
+            }
+            const float inv = 1.f / (den * TC_AUX_UP);
+            cz *= TC_ZP_UP;
 #pragma unroll 1
             for (int c0 = 0; c0 < DH; c0 += 32) {
-                uint32_t raw[32];
-                tmem_ld32(lane_base + P::COL_O + half * DH + c0, raw);
+                uint32_t ra[32], rb[32];
+                tmem_ld32(acc_a + half * DH + c0, ra);
+                if (two) tmem_ld32(acc_b + half * DH + c0, rb);
                 tmem_wait_ld();
                 if (r < nq) {
                     const long long off = b * a.os_b + (long long)(q0 + r) * a.os_l + h * a.os_h + half * DH + c0;
                     float v[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = (__uint_as_float(raw[c]) - corr_row) * inv;
+                    for (int i = 0; i < 32; ++i) {
+                        float s = w_a * __uint_as_float(ra[i]);
+                        if (two) s = fmaf(w_b, __uint_as_float(rb[i]), s);
+                        v[i] = (s - cz) * inv;
+                    }
                     store_o_row32(a.out, a.o_dtype, off, v);
                 }
             }
@@ -696,6 +733,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
         };
         fetch_params(0);
+        // rows 4-15 of the small operand tiles stay zero for the whole kernel
+        for (int i = ptid; i < 4 * P::AUX_BYTES / 16; i += 128) sts128(smem + P::OFF_AUX + i * 16, 0u, 0u, 0u, 0u);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
             const int n_valid = min(N, a.Lk - j * N);
@@ -722,15 +762,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, 128, krows);
                 }
                 if (warp == 8) TC_TRACE(2, j, 3);
-                if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
-                    float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 6 * N;
+                if (ptid < N) {   // slot j % 4 of the tables and of the small operand tile; the K scale carries softmax_scale * log2(e)
+                    float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 3 * N;
                     const float scl = sc * a.scale_log2;
+                    const float vsf = fmaxf(vsc, TC_VS_MIN);
                     tab[ptid] = scl;
-                    tab[N + ptid] = bias;
-                    tab[2 * N + ptid] = bias + __log2f(vsc);
-                    tab[3 * N + ptid] = zs * scl;
-                    tab[4 * N + ptid] = __fdividef(1.f, vsc);
-                    tab[5 * N + ptid] = vzp;
+                    tab[N + ptid] = bias + __log2f(vsf);
+                    tab[2 * N + ptid] = zs * scl;
+                    unsigned char* aux = smem + P::OFF_AUX + (j & 3) * P::AUX_BYTES;
+                    const float vin = TC_AUX_DOWN / vsf, vzd = vzp * TC_ZP_DOWN;
+                    const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
+                    *reinterpret_cast<__half*>(aux + tile_off(0, ptid, 16)) = vin_hi;
+                    *reinterpret_cast<__half*>(aux + tile_off(1, ptid, 16)) = __float2half_rn(vin - __half2float(vin_hi));
+                    *reinterpret_cast<__half*>(aux + tile_off(2, ptid, 16)) = vz_hi;
+                    *reinterpret_cast<__half*>(aux + tile_off(3, ptid, 16)) = __float2half_rn(vzd - __half2float(vz_hi));
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_k[s]);
@@ -816,14 +861,26 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const uint64_t kd0 = smem_desc(smem_u32(smem + P::OFF_K), 16, 1024);
         const uint64_t pd0 = smem_desc(smem_u32(smem + P::OFF_P), 16, 1024);
         const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), N * 128, 1024);
+        constexpr uint32_t IDESC_AUX = instr_desc(TC_M, 16, 0);
+        const uint64_t ad0 = smem_desc(smem_u32(smem + P::OFF_AUX), 16, 1024);
+        // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
+        // half of a tile's keys goes to accumulator 0, the second half to accumulator 1
         auto issue_pv = [&](int j) {
             const int s = j & 1;
             const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
             const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
+            const uint64_t ad = ad0 + (uint64_t)(((j & 3) * P::AUX_BYTES) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < N / 16; ++kk)
-                if (kk < ksteps) tc_mma_f16(tmem_base + P::COL_O, pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
-                           vd + (uint64_t)((kk * 2048) >> 4), IDESC_O, (j > 0 || kk > 0) ? 1u : 0u);
+            for (int kk = 0; kk < N / 16; ++kk) {
+                if (kk < ksteps) {
+                    const int hf = kk >= N / 32 ? 1 : 0;
+                    const uint32_t acc = tmem_base + P::COL_O + hf * P::ACC_COLS;
+                    const uint32_t accum = (j > 0 || kk > hf * (N / 32)) ? 1u : 0u;
+                    const uint64_t pk = pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4);
+                    tc_mma_f16(acc, pk, vd + (uint64_t)((kk * 2048) >> 4), IDESC_O, accum);
+                    tc_mma_f16(acc + D, pk, ad + (uint64_t)(((kk >> 2) * 2048 + (kk & 3) * 32) >> 4), IDESC_AUX, accum);
+                }
+            }
             tc_commit(&bar_pv[s]);
         };
         for (int j = 0; j < T; ++j) {
@@ -841,12 +898,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 #pragma unroll
                 for (int ki = 0; ki < P::KT; ++ki) {
                     if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
+                    const uint64_t qd = qd0 + (uint64_t)((qi * P::Q_BYTES) >> 4), kdk = kd + (uint64_t)((ki * P::KV_BYTES) >> 4);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
-                        tc_mma_f16(tmem_base + P::COL_S + s * N,
-                                   qd0 + (uint64_t)((qi * P::Q_BYTES + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
-                                   kd + (uint64_t)((ki * P::KV_BYTES + (kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S,
-                                   first ? 0u : 1u);
+                        tc_mma_f16(tmem_base + P::COL_S + s * N, qd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                                   kdk + (uint64_t)(((kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S, first ? 0u : 1u);
                         first = false;
                     }
                 }

@@ -476,7 +476,9 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
     float scale[VPW], zp[VPW];
     GroupQ gq[VPW];
     auto fetch = [&](int b, int l) {
-        for (int j = 0; j < np; ++j) {
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) {      // compile-time trip count keeps the per-value parameters in registers
+            if (j >= np) break;
             const int d = min(d0 + j, a.D - 1);
             const long long gid = group_id(a, b, l, h, d);
             Range rg;
@@ -511,15 +513,17 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
-                    const int pj = uniform ? 0 : j;
-                    word |= (quant_code_rt(v[u][j], gq[pj], sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+                    const GroupQ g = uniform ? gq[0] : gq[j];
+                    word |= (quant_code_rt(v[u][j], g, sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
             a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
             // one writer per group: the member with the lowest shared coordinates
             const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
             if (first) {
-                for (int j = 0; j < np; ++j) {
+#pragma unroll
+                for (int j = 0; j < VPW; ++j) {
+                    if (j >= np) break;
                     const int d = d0 + j;
                     if (d < a.D && (d % a.group) == 0) {
                         const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
