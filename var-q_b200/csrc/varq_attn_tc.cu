@@ -1,6 +1,6 @@
 // Attention over the packed cache on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Thirteen warps:
+// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Sixteen warps:
 //   warps 0-7  softmax: two threads share query row r (TMEM lane r), each owning half of every
 //              tile's keys AND its own output accumulator, so the pair never has to agree on a
 //              running maximum: a thread reads its S columns from TMEM 32 at a time, applies the
@@ -10,8 +10,8 @@
 //   warps 8-11 (K) and 12-14 (V) producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
 //              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
 //              K as exact fp16 integer codes, V as fp16 (code - zp) * scale; the K producers also
-//              write the per-key tables and a small operand tile holding 1 / V-scale and the V
-//              zero-point of each key (fp16 hi + lo pairs);
+//              write the per-key tables, the V producers a small operand tile holding 1 / V-scale
+//              and the V zero-point of each key (fp16 hi + lo pairs);
 //   warp  15   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM),
 //              O_half += P V and, with the small tile as B operand, the softmax normaliser
 //              and zero-point correction sum_k P (the tensor core adds up exactly the rounded P
@@ -75,19 +75,18 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the limit expires or another thread has already given up.
-// The loop is inline: a call costs a few hundred cycles of register save / restore around it and
-// puts stack traffic on the critical path of whoever waits.  Only the give-up branch is out of line.
-__device__ __noinline__ bool mbar_give_up(volatile int* abort_flag, int code, uint32_t tries) {
-    if (tries >= TC_SPIN_LIMIT) {
-        *abort_flag = 1;
-        atomicCAS(&g_tc_status, 0, code);
-    }
-    return false;
-}
+// Everything is inline and small: a call here costs a few hundred cycles of register shuffling
+// around it, at every one of the ~20 wait sites, and bloats the loops that hold them.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
     uint32_t tries = 0;
+#pragma unroll 1
     while (!mbar_try(bar, parity)) {     // a failed try_wait has already been suspended by the hardware for a while
-        if (++tries >= TC_SPIN_LIMIT || *abort_flag) return mbar_give_up(abort_flag, code, tries);
+        if (*abort_flag) return false;
+        if (++tries >= TC_SPIN_LIMIT) {
+            *abort_flag = 1;
+            atomicCAS(&g_tc_status, 0, code);
+            return false;
+        }
     }
     return true;
 }
@@ -191,8 +190,8 @@ template <int D, int NQ, bool KS> struct TcPlan {
     static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [PST]
     static constexpr int OFF_PK = OFF_P + PST * P_BYTES;      // [2][K, V]
     static constexpr int AUX_BYTES = (N / 64) * 16 * 128;     // 16 x N fp16, K-major: rows 0-3 = 1/V-scale hi, lo, V zero-point hi, lo
-    static constexpr int OFF_AUX = OFF_PK + 4 * PK_BYTES;     // [4]
-    static constexpr int OFF_KS = OFF_AUX + 4 * AUX_BYTES;    // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
+    static constexpr int OFF_AUX = OFF_PK + 4 * PK_BYTES;     // [2], written with the V stage of the same tile
+    static constexpr int OFF_KS = OFF_AUX + 2 * AUX_BYTES;    // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
     static constexpr int OFF_BAR = OFF_KS + 4 * 3 * N * 4;    // mbarriers
     static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
@@ -387,12 +386,31 @@ __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned
 // four consecutive table entries with one 16-byte shared-memory load (tables are 16-byte aligned)
 __device__ __forceinline__ float4 tab4(const float* p, int c) { return *reinterpret_cast<const float4*>(p + c); }
 
+// A row keeps its reference maximum until a score exceeds it by more than this (log2 units): P stays below
+// 2^12 in fp16 and the accumulators are rescaled rarely.
+constexpr float TC_LAZY = 12.f;
 constexpr float TC_VS_MIN = 9.5367431640625e-07f;     // 2^-20: smallest V scale folded into P as is
 constexpr float TC_AUX_DOWN = 0.015625f;              // 2^-6 on 1 / V-scale so that it stays inside fp16's range
 constexpr float TC_AUX_UP = 64.f;
 constexpr float TC_ZP_DOWN = 0.00390625f;             // 2^-8 on the V zero-point
 constexpr float TC_ZP_UP = 256.f;
 
+// packed fp32 pairs (one instruction for two lanes of work on sm_100)
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // raw scores -> x = s * ks + b2 [- kzs * qsum] in place (log2 domain, V scale folded in); returns their maximum
 template <bool KZ>
 __device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* ks, const float* b2, const float* kzs, float qsum) {
@@ -403,14 +421,16 @@ __device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* k
         float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (KZ) z4 = tab4(kzs, c);
         float x[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            x[i] = fmaf(__uint_as_float(rw[c + i]), pick(s4, i), pick(b4, i));
-            if (KZ) x[i] = fmaf(-pick(z4, i), qsum, x[i]);
-            rw[c + i] = __float_as_uint(x[i]);
+        fma2(x[0], x[1], __uint_as_float(rw[c]), __uint_as_float(rw[c + 1]), s4.x, s4.y, b4.x, b4.y);
+        fma2(x[2], x[3], __uint_as_float(rw[c + 2]), __uint_as_float(rw[c + 3]), s4.z, s4.w, b4.z, b4.w);
+        if (KZ) {
+            fma2(x[0], x[1], -z4.x, -z4.y, qsum, qsum, x[0], x[1]);
+            fma2(x[2], x[3], -z4.z, -z4.w, qsum, qsum, x[2], x[3]);
         }
-        m0 = fmaxf(m0, fmaxf(x[0], x[1]));
-        m1 = fmaxf(m1, fmaxf(x[2], x[3]));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rw[c + i] = __float_as_uint(x[i]);
+        m0 = max3(m0, x[0], x[1]);
+        m1 = max3(m1, x[2], x[3]);
     }
     return fmaxf(m0, m1);
 }
@@ -418,7 +438,9 @@ __device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* k
 __device__ __forceinline__ void chunk_exp(const uint32_t (&x)[32], float m, uint32_t (&ph)[16]) {
 #pragma unroll
     for (int c = 0; c < 32; c += 2) {
-        const __half2 h2 = __floats2half2_rn(ex2(__uint_as_float(x[c]) - m), ex2(__uint_as_float(x[c + 1]) - m));
+        float y0, y1;
+        add2(y0, y1, __uint_as_float(x[c]), __uint_as_float(x[c + 1]), -m, -m);
+        const __half2 h2 = __floats2half2_rn(ex2(y0), ex2(y1));
         ph[c >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
     }
 }
@@ -441,7 +463,7 @@ __device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const floa
                             : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum));
     }
     float alpha = 1.f;
-    if (tm > m_used + 8.f) {
+    if (tm > m_used + TC_LAZY) {
         alpha = ex2(m_used - tm);       // 0 for a row without a reference yet
         m_used = tm;
     }
@@ -476,7 +498,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
     uint64_t* bar_pk = bars;          // [2] packed K rows landed (tx bytes)
-    uint64_t* bar_k = bars + 2;       // [2] K operand tile and per-key tables written (128 producers)
+    uint64_t* bar_k = bars + 2;       // [2] K operand tile written (128 producers)
     uint64_t* bar_v = bars + 4;       // [2] V operand tile written (128 producers)
     uint64_t* bar_s = bars + 6;       // [2] S = Q K^T complete (tcgen05.commit): K stage free again
     uint64_t* bar_p = bars + 8;       // [2] P written, O rescaled (256 softmax threads)
@@ -503,9 +525,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
 
     if (tid == 0) {
+        // the first two packed tiles are requested before anything else; their latency overlaps the rest of the set-up
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_pk[i], 1);
             mbar_init(&bar_pkv[i], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int j = 0; j < 2 && j < T; ++j) {
+            const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
+            mbar_expect_tx(&bar_pk[j], rows * wk * 4);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
+            mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
+        }
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&bar_k[i], 128);
             mbar_init(&bar_v[i], TC_VPROD);
             mbar_init(&bar_s[i], 1);
@@ -516,14 +549,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         for (int i = 0; i < 4; ++i) mbar_init(&bar_t[i], 128);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // the first two packed tiles are requested right away; their latency overlaps the rest of the set-up
-        for (int j = 0; j < 2 && j < T; ++j) {
-            const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
-            mbar_expect_tx(&bar_pk[j], rows * wk * 4);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
-            mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
-        }
     }
     if (tid < 128) s_qsum[tid] = 0.f;
     if (warp == 15) {   // TMEM allocation by one full warp
@@ -590,6 +615,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const float qsum = k_zp ? s_qsum[r] : 0.f;
         float m_used = -FLT_MAX;                            // reference maximum of this thread's keys (log2 domain)
         bool ok = true;
+#ifdef VARQ_ABL_STAGGER
+        if (half == 1) { const long long ts = clock64(); while (clock64() - ts < VARQ_ABL_STAGGER) { } }
+#endif
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
             if (quarter == 0) TC_TRACE(half, j, 5);
@@ -623,8 +651,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     if (quarter == 0 && c == 0) TC_TRACE(half, j, 6);
                     const float cm = k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
                                           : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum);
-                    if (__any_sync(0xffffffffu, cm > m_used + 8.f)) {
-                        // Rare: some row of this warp meets a score more than 2^8 above its reference.  A new
+                    if (m_used == -FLT_MAX) m_used = cm;    // first chunk this thread ever sees: its maximum is the reference
+                    if (__any_sync(0xffffffffu, cm > m_used + TC_LAZY)) {
+                        // Rare: some row of this warp meets a score more than 2^12 above its reference.  A new
                         // reference is taken, the accumulator rescaled, and the tile's chunks are redone
                         // (P of earlier chunks was written against the old reference).
                         m_used = new_reference<D, N>(s_addr, nch, ks, b2, kzs, k_zp, qsum, m_used, acc,
@@ -713,34 +742,28 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
         const bool v_exact = a.vp.group == D;
         // per-key parameters of a tile are fetched one tile ahead so the global-load latency is hidden
-        float nsc = 0.f, nzs = 0.f, nvsc = 1.f, nvzp = 0.f;
+        float nsc = 0.f, nzs = 0.f, nvsc = 1.f;
+        const long long k_par = a.kp.index(b, 0, h, 0), v_par = a.vp.index(b, 0, h, 0);   // (sample, head) part of the parameter index
         auto fetch_params = [&](int j) {
-            nsc = 0.f; nzs = 0.f; nvsc = 1.f; nvzp = 0.f;
+            nsc = 0.f; nzs = 0.f; nvsc = 1.f;
             const int key = j * N + ptid;
             if (j < T && ptid < N && key < a.Lk) {
                 if constexpr (KS) {
                     nsc = 1.f;                       // S needs only softmax_scale * log2(e)
                 } else {
-                    const long long pi = a.kp.index(b, a.kp.row(key), h, 0);
+                    const long long pi = k_par + a.kp.row(key) * a.kp.sr;
                     nsc = __ldg(a.kp.scale + pi);
                     if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
                 }
-                if (v_exact) {
-                    const long long vi = a.vp.index(b, a.vp.row(key), h, 0);
-                    nvsc = __ldg(a.vp.scale + vi);
-                    if (a.vp.zp) nvzp = __ldg(a.vp.zp + vi);
-                }
+                if (v_exact) nvsc = __ldg(a.vp.scale + v_par + a.vp.row(key) * a.vp.sr);
             }
         };
         fetch_params(0);
-        // rows 4-15 of the small operand tiles stay zero for the whole kernel
-        for (int i = ptid; i < 4 * P::AUX_BYTES / 16; i += 128) sts128(smem + P::OFF_AUX + i * 16, 0u, 0u, 0u, 0u);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
             const int n_valid = min(N, a.Lk - j * N);
             if (warp == 8) TC_TRACE(2, j, 0);
-            const float sc = nsc, zs = nzs, vsc = nvsc, vzp = nvzp;
+            const float sc = nsc, zs = nzs, vsc = nvsc;
             const float bias = (ptid < n_valid) ? 0.f : -1e30f;
             fetch_params(j + 1);
             ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
@@ -762,20 +785,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, 128, krows);
                 }
                 if (warp == 8) TC_TRACE(2, j, 3);
-                if (ptid < N) {   // slot j % 4 of the tables and of the small operand tile; the K scale carries softmax_scale * log2(e)
+                if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
                     float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 3 * N;
                     const float scl = sc * a.scale_log2;
                     const float vsf = fmaxf(vsc, TC_VS_MIN);
                     tab[ptid] = scl;
                     tab[N + ptid] = bias + __log2f(vsf);
                     tab[2 * N + ptid] = zs * scl;
-                    unsigned char* aux = smem + P::OFF_AUX + (j & 3) * P::AUX_BYTES;
-                    const float vin = TC_AUX_DOWN / vsf, vzd = vzp * TC_ZP_DOWN;
-                    const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
-                    *reinterpret_cast<__half*>(aux + tile_off(0, ptid, 16)) = vin_hi;
-                    *reinterpret_cast<__half*>(aux + tile_off(1, ptid, 16)) = __float2half_rn(vin - __half2float(vin_hi));
-                    *reinterpret_cast<__half*>(aux + tile_off(2, ptid, 16)) = vz_hi;
-                    *reinterpret_cast<__half*>(aux + tile_off(3, ptid, 16)) = __float2half_rn(vzd - __half2float(vz_hi));
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_k[s]);
@@ -810,10 +826,35 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         bool ok = true;
         int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
         const bool v_exact = a.vp.group == D;
+        // The small operand tile of a stage (16 x N fp16, K-major): row 0/1 = hi/lo of 2^-6 / V scale, row 2/3 =
+        // hi/lo of 2^-8 * V zero-point of each key; rows 4-15 stay zero for the whole kernel.  Each thread looks
+        // after keys ptid and ptid + 96 and fetches their parameters one tile ahead.
+        constexpr int KPT = (N + TC_VPROD - 1) / TC_VPROD;
+        float nvs[KPT], nvz[KPT];
+        const long long v_par = a.vp.index(b, 0, h, 0);     // (sample, head) part of the parameter index
+        auto fetch_v = [&](int j) {
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) {
+                nvs[i] = 1.f; nvz[i] = 0.f;
+                const int kt = ptid + i * TC_VPROD, key = j * N + kt;
+                if (v_exact && j < T && kt < N && key < a.Lk) {
+                    const long long vi = v_par + a.vp.row(key) * a.vp.sr;
+                    nvs[i] = __ldg(a.vp.scale + vi);
+                    if (a.vp.zp) nvz[i] = __ldg(a.vp.zp + vi);
+                }
+            }
+        };
+        fetch_v(0);
+        for (int i = ptid; i < 2 * P::AUX_BYTES / 16; i += TC_VPROD) sts128(smem + P::OFF_AUX + i * 16, 0u, 0u, 0u, 0u);
+        asm volatile("bar.sync 2, 96;" ::: "memory");
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
             const int k0 = j * N;
             const int n_valid = min(N, a.Lk - k0);
+            float vs[KPT], vz[KPT];
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) { vs[i] = nvs[i]; vz[i] = nvz[i]; }
+            fetch_v(j + 1);
             ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
             if (warp == 12) TC_TRACE(2, j, 5);
             if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
@@ -830,6 +871,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
                     else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
                     else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                }
+                unsigned char* aux = smem + P::OFF_AUX + s * P::AUX_BYTES;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    const int kt = ptid + i * TC_VPROD;
+                    if (kt < N) {
+                        const float vin = TC_AUX_DOWN / fmaxf(vs[i], TC_VS_MIN), vzd = vz[i] * TC_ZP_DOWN;
+                        const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
+                        // element (row, kt) of the 16-row tile: rows 0-3 differ in the row offset and the swizzled chunk only
+                        unsigned char* col = aux + (kt >> 6) * (16 * 128) + ((kt & 7) << 1);
+                        const int ch = (kt & 63) >> 3;
+                        *reinterpret_cast<__half*>(col + ((ch ^ 0) << 4)) = vin_hi;
+                        *reinterpret_cast<__half*>(col + 128 + ((ch ^ 1) << 4)) = __float2half_rn(vin - __half2float(vin_hi));
+                        *reinterpret_cast<__half*>(col + 256 + ((ch ^ 2) << 4)) = vz_hi;
+                        *reinterpret_cast<__half*>(col + 384 + ((ch ^ 3) << 4)) = __float2half_rn(vzd - __half2float(vz_hi));
+                    }
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_v[s]);
@@ -851,47 +908,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
         }
     } else if (lane == 0) {
-        // =============================================================== MMA issue (one thread)
+        // =============================================================== MMA issue (one thread of warp 15)
+        // Order: S(0), S(1), then per tile j: wait P(j) -> S(j+2) -> O += P(j) V(j).  S(j+2) reuses the TMEM
+        // columns of S(j), free once P(j) is complete, and goes first because the softmax two tiles ahead
+        // waits for it while nobody waits for the accumulator.
         constexpr uint32_t IDESC_S = instr_desc(TC_M, N, 0);
         constexpr uint32_t IDESC_O = instr_desc(TC_M, D, 1);
-        const uint32_t q_addr = smem_u32(smem + P::OFF_Q);
+        constexpr uint32_t IDESC_AUX = instr_desc(TC_M, 16, 0);
         bool ok = true;
         // descriptors differ from their stage base only in the start-address field (bits 0-13, 16-byte units)
-        const uint64_t qd0 = smem_desc(q_addr, 16, 1024);
+        const uint64_t qd0 = smem_desc(smem_u32(smem + P::OFF_Q), 16, 1024);
         const uint64_t kd0 = smem_desc(smem_u32(smem + P::OFF_K), 16, 1024);
         const uint64_t pd0 = smem_desc(smem_u32(smem + P::OFF_P), 16, 1024);
         const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), N * 128, 1024);
-        constexpr uint32_t IDESC_AUX = instr_desc(TC_M, 16, 0);
         const uint64_t ad0 = smem_desc(smem_u32(smem + P::OFF_AUX), 16, 1024);
-        // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
-        // half of a tile's keys goes to accumulator 0, the second half to accumulator 1
-        auto issue_pv = [&](int j) {
+        // S = Q K^T of tile j.  exact-code K: Q_hi K [+ Q_lo K]; dequantised K: Q_hi K_hi + Q_hi K_lo [+ Q_lo K_hi]
+        auto issue_qk = [&](int j) -> bool {
             const int s = j & 1;
-            const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
-            const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
-            const uint64_t ad = ad0 + (uint64_t)(((j & 3) * P::AUX_BYTES) >> 4);
-#pragma unroll
-            for (int kk = 0; kk < N / 16; ++kk) {
-                if (kk < ksteps) {
-                    const int hf = kk >= N / 32 ? 1 : 0;
-                    const uint32_t acc = tmem_base + P::COL_O + hf * P::ACC_COLS;
-                    const uint32_t accum = (j > 0 || kk > hf * (N / 32)) ? 1u : 0u;
-                    const uint64_t pk = pd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4);
-                    tc_mma_f16(acc, pk, vd + (uint64_t)((kk * 2048) >> 4), IDESC_O, accum);
-                    tc_mma_f16(acc + D, pk, ad + (uint64_t)(((kk >> 2) * 2048 + (kk & 3) * 32) >> 4), IDESC_AUX, accum);
-                }
-            }
-            tc_commit(&bar_pv[s]);
-        };
-        for (int j = 0; j < T; ++j) {
-            const int s = j & 1;
-            TC_TRACE(3, j, 0);
-            ok = mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31);
-            if (!ok) break;
+            if (!mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31)) return false;
             TC_TRACE(3, j, 1);
             tc_fence_after();
             const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
-            // exact-code K: S = Q_hi K [+ Q_lo K]; dequantised K: S = Q_hi K_hi + Q_hi K_lo [+ Q_lo K_hi]
             bool first = true;
 #pragma unroll
             for (int qi = 0; qi < NQ; ++qi) {
@@ -909,25 +946,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
             tc_commit(&bar_s[s]);
             TC_TRACE(3, j, 2);
-            if (j >= 1) {
-                const int sp = (j - 1) & 1;
-                ok = mbar_wait(&bar_p[sp], ((j - 1) >> 1) & 1, abort_flag, 32) &&
-                     mbar_wait(&bar_v[sp], ((j - 1) >> 1) & 1, abort_flag, 34);
+            return true;
+        };
+        // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
+        // half of a tile's keys goes to accumulator 0, the second half to accumulator 1
+        auto issue_pv = [&](int j) {
+            const int s = j & 1;
+            const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
+            const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
+            const uint64_t ad = ad0 + (uint64_t)((s * P::AUX_BYTES) >> 4);
+            // rolled on purpose: the loop is short-lived code that every CTA has to fetch again
+            uint64_t pk = pd, vk = vd, ak = ad;
+#pragma unroll 1
+            for (int kk = 0; kk < ksteps; ++kk) {
+                const int hf = kk >= N / 32 ? 1 : 0;
+                const uint32_t acc = tmem_base + P::COL_O + hf * P::ACC_COLS;
+                const uint32_t accum = (j > 0 || kk > hf * (N / 32)) ? 1u : 0u;
+                tc_mma_f16(acc, pk, vk, IDESC_O, accum);
+                tc_mma_f16(acc + D, pk, ak, IDESC_AUX, accum);
+                // next 16 keys: 32 bytes further in the K-major tiles (a new 64-key block every fourth step), 16 rows in V
+                const bool wrap = (kk & 3) == 3;
+                pk += wrap ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
+                ak += wrap ? (uint64_t)((2048 - 96) >> 4) : 2u;
+                vk += (uint64_t)(2048 >> 4);
+            }
+            tc_commit(&bar_pv[s]);
+        };
+        // iteration jj issues S(jj) for jj < 2 (nothing to wait for) and from then on: wait P(j), S(j + 2), O += P(j) V(j), j = jj - 2
+        for (int jj = 0; jj < T + 2 && ok; ++jj) {
+            const int j = jj - 2;
+            if (j >= 0) {
+                TC_TRACE(3, jj, 0);
+                ok = mbar_wait(&bar_p[j & 1], (j >> 1) & 1, abort_flag, 32);
                 if (!ok) break;
                 TC_TRACE(3, j, 3);
                 tc_fence_after();
-                issue_pv(j - 1);
             }
-        }
-        if (ok) {
-            const int sp = (T - 1) & 1;
-            ok = mbar_wait(&bar_p[sp], ((T - 1) >> 1) & 1, abort_flag, 33) && mbar_wait(&bar_v[sp], ((T - 1) >> 1) & 1, abort_flag, 35);
-            if (ok) {
+            if (jj < T) {
+                ok = issue_qk(jj);
+                if (!ok) break;
+            }
+            if (j >= 0) {
+                ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, 34);
+                if (!ok) break;
                 tc_fence_after();
-                issue_pv(T - 1);
-                tc_commit(bar_o);
+                issue_pv(j);
             }
         }
+        if (ok) tc_commit(bar_o);
         tc_fence_before();
     }
     if (warp == 0) TC_TRACE(3, 30, 4);
