@@ -306,8 +306,8 @@ def run_ours(args):
             ach = nbytes / (top_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
         # DRAM bytes per launch from one ncu capture of this kernel at a quarter of the batch
-        # (profiles/attn_tc_kernel_var_d16_last_scale.md: 39.3 MB read + 0.02 MB written; traffic scales with batch)
-        traffic = 4 * (39276288 + 19968) if (kind, si) == ("attn", len(STEPS_L) - 1) else None
+        # (profiles/attn_tc_kernel_var_d16_last_scale.md: 39.2 MB read + 0.03 MB written; traffic scales with batch)
+        traffic = 4 * (39217664 + 33792) if (kind, si) == ("attn", len(STEPS_L) - 1) else None
         roof.update({"traffic": traffic, "kernel": f"{kind}[scale {si}: l={lq}, cached={lk}]", "launch_ms": top_ms,
                      "share_of_step": share[top] / sum(share.values()), "peak_source": peaks["source"],
                      "timing": "CUDA events around 20 back-to-back launches of this kernel on the step's own state",
