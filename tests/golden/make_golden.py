@@ -58,7 +58,7 @@ def step_inputs(fmt, B, H, c, seed, dtype):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (read-only)")
     args = ap.parse_args()
     Q, P = load_reference(args.reference)
     torch.set_num_threads(4)

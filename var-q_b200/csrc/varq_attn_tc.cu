@@ -524,31 +524,29 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int aq = (nq + 31) >> 5;                  // TMEM lane quarters that hold real queries
     float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
 
-    if (tid == 0) {
-        // the first two packed tiles are requested before anything else; their latency overlaps the rest of the set-up
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bar_pk[i], 1);
-            mbar_init(&bar_pkv[i], 1);
+    if (warp == 0) {
+        // one lane per mbarrier: [0,2) packed K, [2,4) K tile, [4,6) V tile, [6,8) S, [8,10) P, [10,12) O += P V,
+        // 12 all MMAs, [13,17) tables, [17,19) packed V
+        if (lane < P::N_BARS) {
+            const uint32_t count = (lane >= 2 && lane < 4) || (lane >= 13 && lane < 17) ? 128u
+                                 : (lane >= 4 && lane < 6)   ? (uint32_t)TC_VPROD
+                                 : (lane >= 8 && lane < 10)  ? (uint32_t)(64 * aq)     // only the warps that own real query rows take part
+                                                             : 1u;
+            mbar_init(&bars[lane], count);
         }
+        if (lane == 0) *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int j = 0; j < 2 && j < T; ++j) {
-            const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
-            mbar_expect_tx(&bar_pk[j], rows * wk * 4);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
-            mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
+        __syncwarp();
+        if (lane == 0) {
+            // the first two packed tiles are requested right away; their latency overlaps the rest of the set-up
+            for (int j = 0; j < 2 && j < T; ++j) {
+                const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
+                mbar_expect_tx(&bar_pk[j], rows * wk * 4);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
+                mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
+            }
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&bar_k[i], 128);
-            mbar_init(&bar_v[i], TC_VPROD);
-            mbar_init(&bar_s[i], 1);
-            mbar_init(&bar_p[i], 64 * aq);          // only the warps that own real query rows take part
-            mbar_init(&bar_pv[i], 1);
-        }
-        mbar_init(bar_o, 1);
-        for (int i = 0; i < 4; ++i) mbar_init(&bar_t[i], 128);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 128) s_qsum[tid] = 0.f;
     if (warp == 15) {   // TMEM allocation by one full warp
@@ -615,9 +613,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const float qsum = k_zp ? s_qsum[r] : 0.f;
         float m_used = -FLT_MAX;                            // reference maximum of this thread's keys (log2 domain)
         bool ok = true;
-#ifdef VARQ_ABL_STAGGER
-        if (half == 1) { const long long ts = clock64(); while (clock64() - ts < VARQ_ABL_STAGGER) { } }
-#endif
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
             if (quarter == 0) TC_TRACE(half, j, 5);

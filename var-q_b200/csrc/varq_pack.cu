@@ -160,11 +160,60 @@ __global__ void unpack_dequant_kernel(DequantArgs a) {
     }
 }
 
+// Division of n < 2^31 by a fixed divisor d >= 1 as multiply-high + add + shift (Granlund-Montgomery):
+// s = ceil(log2 d), m = floor(2^32 (2^s - d) / d) + 1, n / d = (umulhi(n, m) + n) >> s.
+struct FastDiv {
+    uint32_t m, s, d;
+};
+static FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d;
+    f.s = 0;
+    while ((1ull << f.s) < d) ++f.s;
+    f.m = (uint32_t)(((1ull << 32) * ((1ull << f.s) - d)) / d + 1);
+    return f;
+}
+__device__ __forceinline__ void divmod(uint32_t n, const FastDiv& f, uint32_t& q, uint32_t& r) {
+    q = (__umulhi(n, f.m) + n) >> f.s;
+    r = n - q * f.d;
+}
+
+// Fast path of the kernel above for tensors below 2^31 words: the same word-per-thread mapping (stores of
+// neighbouring lanes stay contiguous) with 32-bit index arithmetic, divisions by multiply-high, and no word
+// that spans two groups.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256) unpack_dequant_w32_kernel(DequantArgs a, unsigned total, FastDiv dW, FastDiv dH, FastDiv dL) {
+    constexpr int VPW = 32 / BITS;
+    const bool h_inner = a.cs_h <= a.cs_l;                       // row enumeration follows the code tensor's memory order
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        unsigned r, w, b, l, h, t;
+        divmod(i, dW, r, w);
+        if (h_inner) { divmod(r, dH, t, h); divmod(t, dL, b, l); }
+        else         { divmod(r, dL, t, l); divmod(t, dH, b, h); }
+        const uint32_t word = (uint32_t)__ldg(a.codes + b * a.cs_b + l * a.cs_l + h * a.cs_h + w);
+        const long long pi = a.p.index((int)b, a.p.row((int)l), (int)h, (int)(w * VPW));
+        const float s = __ldg(a.p.scale + pi);
+        const float z = a.p.zp ? __ldg(a.p.zp + pi) : 0.0f;
+        float v[VPW];
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) v[j] = __fmul_rn(__fsub_rn((float)field<BITS>(word, j), z), s);
+        store_vals<T, VPW, true>(reinterpret_cast<T*>(a.out) + b * a.os_b + l * a.os_l + h * a.os_h + w * VPW, v, VPW);
+    }
+}
+
 template <typename T, int BITS>
 static int launch_dequant(const DequantArgs& a, bool vec, cudaStream_t st) {
     const long long total = (long long)a.B * a.L * a.H * a.words;
     if (total == 0) return VARQ_OK;
     const int threads = 256;
+    constexpr int VPW = 32 / BITS;
+    if (vec && a.D == a.words * VPW && (a.p.group % VPW) == 0 && total < (1ll << 31)) {
+        unpack_dequant_w32_kernel<T, BITS><<<grid_for(total, threads), threads, 0, st>>>(
+            a, (unsigned)total, make_fastdiv((uint32_t)a.words), make_fastdiv((uint32_t)a.H), make_fastdiv((uint32_t)a.L));
+        VARQ_CUDA_TRY(cudaGetLastError());
+        count_launches(1);
+        return VARQ_OK;
+    }
     const int blocks = grid_for(total, threads);
     if (vec) unpack_dequant_kernel<T, BITS, true><<<blocks, threads, 0, st>>>(a);
     else     unpack_dequant_kernel<T, BITS, false><<<blocks, threads, 0, st>>>(a);
