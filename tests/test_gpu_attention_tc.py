@@ -155,3 +155,27 @@ def test_groupings_whose_k_scale_varies_along_head_dim(D, q_dtype, kkw, vkw, kb,
     out, launches = run("tc", q.to(DEV), kq, vq, scale)
     assert launches == 1
     check(out, O.attention(q, kd, vd, fmt, scale), f"D={D} {q_dtype} K{kkw} V{vkw} {kb}/{vb}")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("symmetric", [True, False])
+def test_all_zero_and_tiny_value_tokens_keep_their_attention_weight(D, symmetric):
+    """A token whose V row is all zeros (its scale is the eps clamp) or tiny still takes its share of the
+    softmax normaliser: the V scale is folded into P, so such a key must not vanish from the row sum.
+    Queries are aligned with those keys so that they carry most of the attention weight."""
+    B, H, Lk, Lq = 1, 2, 300, 160
+    g = torch.Generator().manual_seed(77 + D)
+    k = torch.randn((B, H, Lk, D), generator=g)
+    v = torch.randn((B, H, Lk, D), generator=g)
+    zero_tok, tiny_tok = [3, 70, 130, 299], [5, 64, 200]
+    v[:, :, zero_tok, :] = 0.0
+    v[:, :, tiny_tok, :] *= 1e-6
+    q = torch.randn((B, H, Lq, D), generator=g)
+    q[:, :, :40, :] = 3.0 * k[:, :, 3:4, :] / k[:, :, 3:4, :].norm(dim=-1, keepdim=True) * D ** 0.5      # attends to a zero-V token
+    q[:, :, 40:80, :] = 3.0 * k[:, :, 200:201, :] / k[:, :, 200:201, :].norm(dim=-1, keepdim=True) * D ** 0.5   # and to a tiny one
+    kq, vq = VAR_Q(8, "BHLc", "G_TOKEN_HEAD", symmetric=symmetric), VAR_Q(8, "BHLc", "G_TOKEN_HEAD", symmetric=symmetric)
+    kr, vr = O.OracleVARQ(8, "BHLc", "G_TOKEN_HEAD", symmetric=symmetric), O.OracleVARQ(8, "BHLc", "G_TOKEN_HEAD", symmetric=symmetric)
+    kq.append(k.to(DEV)); vq.append(v.to(DEV))
+    kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    out, _ = run("tc", q.to(DEV), kq, vq, 1.0 / D ** 0.5)
+    check(out, O.attention(q, kd, vd, "BHLc", 1.0 / D ** 0.5).transpose(1, 2), f"zero/tiny V tokens D={D} sym={symmetric}")
