@@ -54,6 +54,7 @@ def make_inputs(device, seed=0, pin_host=False):
         q = torch.nn.functional.normalize(qkv[:, :, 0], dim=-1) * Q_GAIN
         k = torch.nn.functional.normalize(qkv[:, :, 1], dim=-1)
         rec = {"q": q.contiguous(), "k": k.contiguous(), "qkv16": qkv.to(torch.bfloat16).contiguous()}
+        rec["v16"] = rec["qkv16"][:, :, 2].contiguous()     # the V third alone: what the end-to-end leg uploads
         if pin_host:
             rec = {n: t.pin_memory() for n, t in rec.items()}
         out.append(rec)
@@ -107,23 +108,42 @@ def hot_path_step(inputs, probe=None):
     return out
 
 
-def e2e_step(host_inputs, device, dev_bufs, host_out):
-    """Same path through the public API with HOST buffers: every call's inputs are copied from
-    pinned host memory and its result is copied back, inside the timed region."""
+def e2e_step(host_inputs, device, dev_bufs, host_out, side=None):
+    """Same path through the public API with HOST buffers: every call's inputs (q and k in fp32, v in
+    bf16) are copied from pinned host memory and its result is copied back, inside the timed region.  The copies run
+    on two side streams (`side` = (h2d_stream, d2h_stream)) so that the upload of the next call,
+    this call's kernels and the download of the previous result overlap; every buffer reuse is
+    ordered by events, and the calling stream joins both side streams before returning."""
     from VAR_Q.attention import attend_cached
+    main = torch.cuda.current_stream(device)
+    up, down = side if side is not None else (main, main)
     h2d = d2h = 0
+    in_free = [None] * len(host_inputs)          # recorded on `main` once a scale's device inputs have been consumed
     for kq, vq in new_quantizers():
         for si, rec in enumerate(host_inputs):
             buf = dev_bufs[si]
-            buf["q"].copy_(rec["q"], non_blocking=True)
-            buf["k"].copy_(rec["k"], non_blocking=True)
-            buf["qkv16"].copy_(rec["qkv16"], non_blocking=True)
-            h2d += rec["q"].numel() * 4 + rec["k"].numel() * 4 + rec["qkv16"].numel() * 2
+            with torch.cuda.stream(up):
+                if in_free[si] is not None:
+                    up.wait_event(in_free[si])
+                buf["q"].copy_(rec["q"], non_blocking=True)
+                buf["k"].copy_(rec["k"], non_blocking=True)
+                buf["v16"].copy_(rec["v16"], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(up)
+            h2d += rec["q"].numel() * 4 + rec["k"].numel() * 4 + rec["v16"].numel() * 2
+            main.wait_event(ready)
             kq.append(buf["k"])
-            vq.append(buf["v"])
+            vq.append(buf["v16"])
             out = attend_cached(buf["q"], kq, vq, 1.0, out_dtype=torch.bfloat16)
-            host_out[si].copy_(out, non_blocking=True)
+            in_free[si] = torch.cuda.Event()
+            in_free[si].record(main)
+            down.wait_event(in_free[si])
+            with torch.cuda.stream(down):
+                host_out[si].copy_(out, non_blocking=True)
+            out.record_stream(down)
             d2h += out.numel() * 2
+    main.wait_stream(up)
+    main.wait_stream(down)
     return h2d, d2h
 
 
@@ -269,17 +289,17 @@ def run_ours(args):
     top_ms = k0.elapsed_time(k1) / reps
 
     # ---- end to end with host buffers
-    dev_bufs = [{"q": torch.empty_like(r["q"]), "k": torch.empty_like(r["k"]), "qkv16": torch.empty_like(r["qkv16"])} for r in inputs]
-    for b in dev_bufs:
-        b["v"] = b["qkv16"].unbind(dim=2)[2]
+    dev_bufs = [{"q": torch.empty_like(r["q"]), "k": torch.empty_like(r["k"]), "v16": torch.empty_like(r["v"], memory_format=torch.contiguous_format)}
+                for r in inputs]
     host_out = [torch.empty((B2, l, HEADS, HEAD_DIM), dtype=torch.bfloat16).pin_memory() for l in STEPS_L]
     e2e_steps = max(1, min(args.steps, 2))
-    e2e_step(host_inputs, device, dev_bufs, host_out)
+    side = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    e2e_step(host_inputs, device, dev_bufs, host_out, side)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        h2d, d2h = e2e_step(host_inputs, device, dev_bufs, host_out)
+        h2d, d2h = e2e_step(host_inputs, device, dev_bufs, host_out, side)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
