@@ -282,6 +282,30 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
     }
 }
 
+// Scale and zero-point of the VPW values of one packed word, kept in registers while consecutive keys of
+// a thread share their parameter row (groupings with one row per appended step): a thread always converts
+// the same word column of every key it visits, so the parameters change only when the row does.
+template <int VPW> struct WordParams {
+    float s[VPW], z[VPW];
+    int row;
+    __device__ __forceinline__ void fetch(const ParamView& pv, int b, int r, int h, int d0, bool uniform) {
+        row = r;
+        if (uniform) {
+            const long long pi = pv.index(b, r, h, d0);
+            const float sv = __ldg(pv.scale + pi), zv = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) { s[j] = sv; z[j] = zv; }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                const long long pi = pv.index(b, r, h, d0 + j);
+                s[j] = __ldg(pv.scale + pi);
+                z[j] = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+            }
+        }
+    }
+};
+
 // Convert `BITS`-wide codes of one packed word to fp16 and write them to the operand tile.
 // EXACT: raw integer codes; otherwise (code - z) * s.
 // General V path: (code - zp) * scale in fp32, rounded to fp16, for groupings whose scale varies along
@@ -293,27 +317,18 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
     const int total = min(N, (n_valid + 31) & ~31) * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
     const bool uniform = (pv.group % VPW) == 0;
+    const bool fixed_w = (nthr & (W - 1)) == 0;      // this thread's word column never changes
+    WordParams<VPW> wp;
+    wp.row = -1;
     for (int idx = ptid; idx < total; idx += nthr) {
         const int key = idx >> wshift, w = idx & (W - 1);
         __half hv[VPW];
         if (key < n_valid) {
             const uint32_t word = packed[idx];
             const int row = pv.row(k0 + key);
-            float s = 0.f, z = 0.f;
-            if (uniform) {
-                const long long pi = pv.index(b, row, h, w * VPW);
-                s = __ldg(pv.scale + pi);
-                z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
-            }
+            if (row != wp.row || !fixed_w) wp.fetch(pv, b, row, h, w * VPW, uniform);
 #pragma unroll
-            for (int j = 0; j < VPW; ++j) {
-                if (!uniform) {
-                    const long long pi = pv.index(b, row, h, w * VPW + j);
-                    s = __ldg(pv.scale + pi);
-                    z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
-                }
-                hv[j] = __float2half_rn(((float)field<BITS>(word, j) - z) * s);
-            }
+            for (int j = 0; j < VPW; ++j) hv[j] = __float2half_rn(((float)field<BITS>(word, j) - wp.z[j]) * wp.s[j]);
         } else {
 #pragma unroll
             for (int j = 0; j < VPW; ++j) hv[j] = __float2half_rn(0.f);
@@ -339,26 +354,19 @@ __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned
     const int total = N * W;
     const int wshift = __ffs(W) - 1;
     const bool uniform = (pv.group % VPW) == 0;
+    const bool fixed_w = (128 & (W - 1)) == 0;       // this thread's word column never changes
+    WordParams<VPW> wp;
+    wp.row = -1;
     for (int idx = ptid; idx < total; idx += 128) {
         const int key = idx >> wshift, w = idx & (W - 1);
         __half hh[VPW], hl[VPW];
         if (key < n_valid) {
             const uint32_t word = packed[idx];
             const int row = pv.row(k0 + key);
-            float s = 0.f, z = 0.f;
-            if (uniform) {
-                const long long pi = pv.index(b, row, h, w * VPW);
-                s = __ldg(pv.scale + pi);
-                z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
-            }
+            if (row != wp.row || !fixed_w) wp.fetch(pv, b, row, h, w * VPW, uniform);
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
-                if (!uniform) {
-                    const long long pi = pv.index(b, row, h, w * VPW + j);
-                    s = __ldg(pv.scale + pi);
-                    z = pv.zp ? __ldg(pv.zp + pi) : 0.f;
-                }
-                const float k = ((float)field<BITS>(word, j) - z) * s;
+                const float k = ((float)field<BITS>(word, j) - wp.z[j]) * wp.s[j];
                 hh[j] = __float2half_rn(k);
                 hl[j] = __float2half_rn(k - __half2float(hh[j]));
             }
