@@ -340,29 +340,60 @@ __device__ __forceinline__ void stats_flush(uint32_t* stats, long long gid, cons
     if (!sym) atomicMax(&stats[gid * 2 + 1], r.lo);
 }
 
+// Rows r, r + step, r + 2 step, ... of the (batch, token) plane without a division per row: (b, l) and the
+// element / word offsets of the row advance incrementally, with one carry when l wraps.
+struct RowIter {
+    unsigned r, b, l, L, step, step_b, step_l;
+    long long xoff, coff, x_step, c_step, x_carry, c_carry;
+    __device__ __forceinline__ void init(const QuantArgs& a, unsigned r0, unsigned r_step) {
+        L = (unsigned)a.L; step = r_step; r = r0;
+        b = r0 / L; l = r0 - b * L;
+        step_b = r_step / L; step_l = r_step - step_b * L;
+        xoff = b * a.xs_b + l * a.xs_l; coff = b * a.cs_b + l * a.cs_l;
+        x_step = step_b * a.xs_b + step_l * a.xs_l; c_step = step_b * a.cs_b + step_l * a.cs_l;
+        x_carry = a.xs_b - (long long)L * a.xs_l; c_carry = a.cs_b - (long long)L * a.cs_l;
+    }
+    __device__ __forceinline__ void next() {
+        r += step; b += step_b; l += step_l; xoff += x_step; coff += c_step;
+        if (l >= L) { l -= L; ++b; xoff += x_carry; coff += c_carry; }
+    }
+};
+
+// min / max of a group member set in float registers; the order-preserving integer form is produced once
+struct FRange { float hi, lo; };
+template <bool SYM> __device__ __forceinline__ void frange_init(FRange& r) { r.hi = SYM ? 0.f : -INFINITY; r.lo = INFINITY; }
+template <bool SYM> __device__ __forceinline__ void frange_add(FRange& r, float v) {
+    if (SYM) r.hi = fmaxf(r.hi, fabsf(v));
+    else { r.hi = fmaxf(r.hi, v); r.lo = fminf(r.lo, v); }
+}
+template <bool SYM> __device__ __forceinline__ Range frange_ord(const FRange& r) {
+    Range o;
+    o.hi = f2ord(r.hi);
+    o.lo = SYM ? 0u : ~f2ord(r.lo);
+    return o;
+}
+
 constexpr int TAB_UNROLL = 4;   // independent row loads in flight per thread
 
-template <typename T, int STORE_BITS, bool VEC>
-__global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters) {
+template <typename T, int STORE_BITS, bool VEC, bool SYM>
+__device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, uint32_t* s_fold) {
     constexpr int VPW = 32 / STORE_BITS;
-    extern __shared__ uint32_t s_fold[];            // [blockDim.x * VPW][2] when rows are folded in the block
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     const bool col_ok = cs < a.H * a.words;
     const int h = col_ok ? cs / a.words : 0, w = col_ok ? cs % a.words : 0;
     const int d0 = w * VPW;
     const int n_valid = min(VPW, a.D - d0);
-    const bool sym = a.symmetric != 0;
     const bool uniform = (a.group % VPW) == 0;      // one group per thread-vector
     const bool row_dep = !(a.share_b && a.share_l); // group depends on the (b, l) row
     const unsigned R = (unsigned)a.B * (unsigned)a.L;       // host guarantees < 2^31
-    const unsigned r_step = gridDim.y * blockDim.y;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
-    Range acc[VPW];
+    FRange acc[VPW];
 #pragma unroll
-    for (int j = 0; j < VPW; ++j) range_init(acc[j]);
+    for (int j = 0; j < VPW; ++j) frange_init<SYM>(acc[j]);
 
-    unsigned r = blockIdx.y * blockDim.y + threadIdx.y;
+    RowIter ri;
+    ri.init(a, blockIdx.y * blockDim.y + threadIdx.y, gridDim.y * blockDim.y);
     if (!row_dep) {
         // ---- statistics do not depend on the row: accumulate in registers, several loads in flight
         for (int it = 0; it < iters; it += TAB_UNROLL) {
@@ -370,34 +401,39 @@ __global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters
             bool ok[TAB_UNROLL];
 #pragma unroll
             for (int u = 0; u < TAB_UNROLL; ++u) {
-                const unsigned ru = r + u * r_step;
-                ok[u] = col_ok && it + u < iters && ru < R;
-                if (ok[u]) {
-                    const unsigned b = ru / (unsigned)a.L, l = ru - b * (unsigned)a.L;
-                    load_vals<T, VPW, VEC>(xcol + b * a.xs_b + l * a.xs_l, v[u], n_valid);
-                }
+                ok[u] = col_ok && it + u < iters && ri.r < R;
+                if (ok[u]) load_vals<T, VPW, VEC>(xcol + ri.xoff, v[u], n_valid);
+                ri.next();
             }
 #pragma unroll
             for (int u = 0; u < TAB_UNROLL; ++u) {
                 if (!ok[u]) continue;
 #pragma unroll
                 for (int j = 0; j < VPW; ++j)
-                    if (j < n_valid) range_add(acc[uniform ? 0 : j], v[u][j], sym);
+                    if (j < n_valid) frange_add<SYM>(acc[uniform ? 0 : j], v[u][j]);
             }
-            r += TAB_UNROLL * r_step;
         }
+        Range ord[VPW];
+#pragma unroll
+        for (int j = 0; j < VPW; ++j) ord[j] = frange_ord<SYM>(acc[j]);
         // fold the block's rows in shared memory, then one global atomic per column and block
         const int np = uniform ? 1 : VPW;
         if (blockDim.y > 1) {
             for (int i = threadIdx.y * blockDim.x + threadIdx.x; i < (int)blockDim.x * VPW * 2; i += blockDim.x * blockDim.y) s_fold[i] = 0u;
             __syncthreads();
-            for (int j = 0; j < np; ++j) {
-                atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2], acc[j].hi);
-                if (!sym) atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2 + 1], acc[j].lo);
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (j >= np) break;
+                atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2], ord[j].hi);
+                if (!SYM) atomicMax(&s_fold[(threadIdx.x * VPW + j) * 2 + 1], ord[j].lo);
             }
             __syncthreads();
             if (threadIdx.y != 0) return;
-            for (int j = 0; j < np; ++j) { acc[j].hi = s_fold[(threadIdx.x * VPW + j) * 2]; acc[j].lo = s_fold[(threadIdx.x * VPW + j) * 2 + 1]; }
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                if (j >= np) break;
+                ord[j].hi = s_fold[(threadIdx.x * VPW + j) * 2]; ord[j].lo = s_fold[(threadIdx.x * VPW + j) * 2 + 1];
+            }
         }
         if (uniform) {
             const long long gid = col_ok ? group_id(a, 0, 0, h, d0) : -1;
@@ -406,72 +442,79 @@ __global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters
             if (same && __activemask() == 0xffffffffu) {
                 if (gid >= 0) {
                     Range t;
-                    t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
-                    t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
-                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, sym);
+                    t.hi = __reduce_max_sync(0xffffffffu, ord[0].hi);
+                    t.lo = __reduce_max_sync(0xffffffffu, ord[0].lo);
+                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, SYM);
                 }
             } else if (col_ok) {
-                stats_flush(a.stats, gid, acc[0], sym);
+                stats_flush(a.stats, gid, ord[0], SYM);
             }
         } else if (col_ok) {
 #pragma unroll
             for (int j = 0; j < VPW; ++j)
-                if (j < n_valid) stats_flush(a.stats, group_id(a, 0, 0, h, d0 + j), acc[j], sym);
+                if (j < n_valid) stats_flush(a.stats, group_id(a, 0, 0, h, d0 + j), ord[j], SYM);
         }
         return;
     }
     // ---- statistics depend on the row: flush after every row, warp-aggregated when a warp sits in one group
-    for (int it = 0; it < iters; ++it, r += r_step) {
-        const bool ok = col_ok && r < R;
-        int b = 0, l = 0;
+    for (int it = 0; it < iters; ++it, ri.next()) {
+        const bool ok = col_ok && ri.r < R;
+        const int b = (int)ri.b, l = (int)ri.l;
         if (ok) {
-            b = (int)(r / (unsigned)a.L); l = (int)(r - (unsigned)b * (unsigned)a.L);
             float v[VPW];
-            load_vals<T, VPW, VEC>(xcol + b * a.xs_b + l * a.xs_l, v, n_valid);
+            load_vals<T, VPW, VEC>(xcol + ri.xoff, v, n_valid);
 #pragma unroll
             for (int j = 0; j < VPW; ++j)
-                if (j < n_valid) range_add(acc[uniform ? 0 : j], v[j], sym);
+                if (j < n_valid) frange_add<SYM>(acc[uniform ? 0 : j], v[j]);
         }
         if (uniform) {
             const long long gid = ok ? group_id(a, b, l, h, d0) : -1;
+            const Range mine = frange_ord<SYM>(acc[0]);
             int same;
             __match_all_sync(0xffffffffu, gid, &same);
             if (same) {
                 if (gid >= 0) {
                     Range t;
-                    t.hi = __reduce_max_sync(0xffffffffu, acc[0].hi);
-                    t.lo = __reduce_max_sync(0xffffffffu, acc[0].lo);
-                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, sym);
+                    t.hi = __reduce_max_sync(0xffffffffu, mine.hi);
+                    t.lo = __reduce_max_sync(0xffffffffu, mine.lo);
+                    if ((threadIdx.x & 31) == 0) stats_flush(a.stats, gid, t, SYM);
                 }
             } else if (ok) {
-                stats_flush(a.stats, gid, acc[0], sym);
+                stats_flush(a.stats, gid, mine, SYM);
             }
-            range_init(acc[0]);
+            frange_init<SYM>(acc[0]);
         } else if (ok) {
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
-                if (j < n_valid) stats_flush(a.stats, group_id(a, b, l, h, d0 + j), acc[j], sym);
-                range_init(acc[j]);
+                if (j < n_valid) stats_flush(a.stats, group_id(a, b, l, h, d0 + j), frange_ord<SYM>(acc[j]), SYM);
+                frange_init<SYM>(acc[j]);
             }
         }
     }
 }
 
 template <typename T, int STORE_BITS, bool VEC>
-__global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters) {
+__global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters) {
+    extern __shared__ uint32_t s_fold[];            // [blockDim.x * VPW][2] when rows are folded in the block
+    if (a.symmetric) quant_stats_body<T, STORE_BITS, VEC, true>(a, iters, s_fold);
+    else             quant_stats_body<T, STORE_BITS, VEC, false>(a, iters, s_fold);
+}
+
+template <typename T, int STORE_BITS, bool VEC, bool SYM>
+__device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
+    constexpr int UN = TAB_UNROLL;
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     if (cs >= a.H * a.words) return;
     const int h = cs / a.words, w = cs % a.words;
     const int d0 = w * VPW;
     const int n_valid = min(VPW, a.D - d0);
-    const bool sym = a.symmetric != 0;
     const bool uniform = (a.group % VPW) == 0;
     const bool row_dep = !(a.share_b && a.share_l);
     const unsigned R = (unsigned)a.B * (unsigned)a.L;
-    const unsigned r_step = gridDim.y * blockDim.y;
     const int np = uniform ? 1 : VPW;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
+    int32_t* ccol = a.codes + h * a.cs_h + w;
 
     float scale[VPW], zp[VPW];
     GroupQ gq[VPW];
@@ -484,28 +527,28 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             Range rg;
             rg.hi = a.stats[gid * 2];
             rg.lo = a.stats[gid * 2 + 1];
-            params_from_range(rg, a.bits, sym, a.eps, scale[j], zp[j]);
+            params_from_range(rg, a.bits, SYM, a.eps, scale[j], zp[j]);
             gq[j] = make_group_q(scale[j], zp[j], a.bits);
         }
     };
     if (!row_dep) fetch(0, 0);
 
-    unsigned r = blockIdx.y * blockDim.y + threadIdx.y;
-    for (int it = 0; it < iters; it += TAB_UNROLL, r += TAB_UNROLL * r_step) {
-        float v[TAB_UNROLL][VPW];
-        unsigned rb[TAB_UNROLL], rl[TAB_UNROLL];
-        bool ok[TAB_UNROLL];
+    RowIter ri;
+    ri.init(a, blockIdx.y * blockDim.y + threadIdx.y, gridDim.y * blockDim.y);
+    for (int it = 0; it < iters; it += UN) {
+        float v[UN][VPW];
+        unsigned rb[UN], rl[UN];
+        long long co[UN];
+        bool ok[UN];
 #pragma unroll
-        for (int u = 0; u < TAB_UNROLL; ++u) {
-            const unsigned ru = r + u * r_step;
-            ok[u] = it + u < iters && ru < R;
-            if (ok[u]) {
-                rb[u] = ru / (unsigned)a.L; rl[u] = ru - rb[u] * (unsigned)a.L;
-                load_vals<T, VPW, VEC>(xcol + rb[u] * a.xs_b + rl[u] * a.xs_l, v[u], n_valid);
-            }
+        for (int u = 0; u < UN; ++u) {
+            ok[u] = it + u < iters && ri.r < R;
+            rb[u] = ri.b; rl[u] = ri.l; co[u] = ri.coff;
+            if (ok[u]) load_vals<T, VPW, VEC>(xcol + ri.xoff, v[u], n_valid);
+            ri.next();
         }
 #pragma unroll
-        for (int u = 0; u < TAB_UNROLL; ++u) {
+        for (int u = 0; u < UN; ++u) {
             if (!ok[u]) continue;
             const int b = (int)rb[u], l = (int)rl[u];
             if (row_dep) fetch(b, l);
@@ -514,10 +557,10 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
                     const GroupQ g = uniform ? gq[0] : gq[j];
-                    word |= (quant_code_rt(v[u][j], g, sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+                    word |= (quant_code<SYM>(v[u][j], g) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
-            a.codes[b * a.cs_b + l * a.cs_l + h * a.cs_h + w] = (int32_t)word;
+            ccol[co[u]] = (int32_t)word;
             // one writer per group: the member with the lowest shared coordinates
             const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
             if (first) {
@@ -528,12 +571,18 @@ __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters
                     if (d < a.D && (d % a.group) == 0) {
                         const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
                         a.scale[pi] = scale[j];
-                        if (!sym) a.zp[pi] = zp[j];
+                        if (!SYM) a.zp[pi] = zp[j];
                     }
                 }
             }
         }
     }
+}
+
+template <typename T, int STORE_BITS, bool VEC>
+__global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters) {
+    if (a.symmetric) quant_apply_body<T, STORE_BITS, VEC, true>(a, iters);
+    else             quant_apply_body<T, STORE_BITS, VEC, false>(a, iters);
 }
 
 // ---------------------------------------------------------------- host side
