@@ -347,7 +347,7 @@ def run_ours(args):
             "roofline": roof,
         }
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(sample_blocks=2)
+            line["cpu_baseline"] = cpu_baseline(sample_blocks=12)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -387,9 +387,9 @@ def run_reference(args):
     torch.set_num_threads(cores)
     host_inputs = make_inputs(None, seed=0)
     blocks = 1
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(min(args.warmup, 3)):
         cpu_blocks(host_inputs, blocks)
-    steps = max(1, min(args.steps, 3))
+    steps = max(1, min(args.steps, 60))          # one block is about a second of all host cores
     t0 = time.perf_counter()
     for _ in range(steps):
         cpu_blocks(host_inputs, blocks)
@@ -398,7 +398,7 @@ def run_reference(args):
     sample = f"each step = {blocks} of {DEPTH} blocks of the workload on {cores} host threads, scaled by {DEPTH}/{blocks}; {steps} steps timed"
     print(json.dumps({
         "impl": "reference", "metric": "kv_hot_path_images_per_sec", "value": value, "unit": "images/s",
-        "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * DEPTH / blocks * 1e3,
+        "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": dt * DEPTH / blocks * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference algorithm (the reference is Python and cannot travel to the GPU box)"},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},

@@ -179,24 +179,38 @@ __device__ __forceinline__ void divmod(uint32_t n, const FastDiv& f, uint32_t& q
 }
 
 // Fast path of the kernel above for tensors below 2^31 words: the same word-per-thread mapping (stores of
-// neighbouring lanes stay contiguous) with 32-bit index arithmetic, divisions by multiply-high, and no word
-// that spans two groups.
+// neighbouring lanes stay contiguous) with 32-bit index arithmetic and divisions by multiply-high.
 template <typename T, int BITS>
 __global__ void __launch_bounds__(256) unpack_dequant_w32_kernel(DequantArgs a, unsigned total, FastDiv dW, FastDiv dH, FastDiv dL) {
     constexpr int VPW = 32 / BITS;
     const bool h_inner = a.cs_h <= a.cs_l;                       // row enumeration follows the code tensor's memory order
+    const bool uniform = (a.p.group % VPW) == 0;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         unsigned r, w, b, l, h, t;
         divmod(i, dW, r, w);
         if (h_inner) { divmod(r, dH, t, h); divmod(t, dL, b, l); }
         else         { divmod(r, dL, t, l); divmod(t, dH, b, h); }
         const uint32_t word = (uint32_t)__ldg(a.codes + b * a.cs_b + l * a.cs_l + h * a.cs_h + w);
-        const long long pi = a.p.index((int)b, a.p.row((int)l), (int)h, (int)(w * VPW));
-        const float s = __ldg(a.p.scale + pi);
-        const float z = a.p.zp ? __ldg(a.p.zp + pi) : 0.0f;
+        const int row = a.p.row((int)l);
         float v[VPW];
+        if (uniform) {
+            const long long pi = a.p.index((int)b, row, (int)h, (int)(w * VPW));
+            const float s = __ldg(a.p.scale + pi);
+            const float z = a.p.zp ? __ldg(a.p.zp + pi) : 0.0f;
 #pragma unroll
-        for (int j = 0; j < VPW; ++j) v[j] = __fmul_rn(__fsub_rn((float)field<BITS>(word, j), z), s);
+            for (int j = 0; j < VPW; ++j) v[j] = __fmul_rn(__fsub_rn((float)field<BITS>(word, j), z), s);
+        } else {
+            // a word spans several groups (per-dim parameters): one parameter pair per value
+            const long long p0 = a.p.index((int)b, row, (int)h, 0);
+#pragma unroll
+            for (int j = 0; j < VPW; ++j) {
+                const int d = (int)(w * VPW) + j;
+                const long long pi = p0 + (long long)(a.p.group == 1 ? d : d / a.p.group) * a.p.sg;
+                const float s = __ldg(a.p.scale + pi);
+                const float z = a.p.zp ? __ldg(a.p.zp + pi) : 0.0f;
+                v[j] = __fmul_rn(__fsub_rn((float)field<BITS>(word, j), z), s);
+            }
+        }
         store_vals<T, VPW, true>(reinterpret_cast<T*>(a.out) + b * a.os_b + l * a.os_l + h * a.os_h + w * VPW, v, VPW);
     }
 }
@@ -207,7 +221,7 @@ static int launch_dequant(const DequantArgs& a, bool vec, cudaStream_t st) {
     if (total == 0) return VARQ_OK;
     const int threads = 256;
     constexpr int VPW = 32 / BITS;
-    if (vec && a.D == a.words * VPW && (a.p.group % VPW) == 0 && total < (1ll << 31)) {
+    if (vec && a.D == a.words * VPW && total < (1ll << 31)) {
         unpack_dequant_w32_kernel<T, BITS><<<grid_for(total, threads), threads, 0, st>>>(
             a, (unsigned)total, make_fastdiv((uint32_t)a.words), make_fastdiv((uint32_t)a.H), make_fastdiv((uint32_t)a.L));
         VARQ_CUDA_TRY(cudaGetLastError());
