@@ -90,6 +90,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
     return true;
 }
+// Three barriers polled together: their probes are independent, so the latencies overlap instead of adding up
+// (the third one is optional).  Same bound and abort rules as mbar_wait.
+__device__ __forceinline__ bool mbar_wait3(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2, bool use2,
+                                           volatile int* abort_flag, int code) {
+    uint32_t tries = 0;
+#pragma unroll 1
+    while (true) {
+        const bool d0 = mbar_try(b0, p0), d1 = mbar_try(b1, p1), d2 = use2 ? mbar_try(b2, p2) : true;
+        if (d0 && d1 && d2) return true;
+        if (*abort_flag) return false;
+        if (++tries >= TC_SPIN_LIMIT) {
+            *abort_flag = 1;
+            atomicCAS(&g_tc_status, 0, code);
+            return false;
+        }
+    }
+}
 __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -624,8 +641,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
             if (quarter == 0) TC_TRACE(half, j, 5);
-            ok = ok && mbar_wait(&bar_t[j & 3], (j >> 2) & 1, abort_flag, 10);   // per-key tables are visible
-            ok = ok && mbar_wait(&bar_s[buf], (j >> 1) & 1, abort_flag, 11);
+            // per-key tables visible, S complete, and the P buffer free (the MMA that read it two tiles ago is done)
+            ok = ok && mbar_wait3(&bar_t[j & 3], (j >> 2) & 1, &bar_s[buf], (j >> 1) & 1,
+                                  &bar_pv[(j - P::PST) & 1], ((j - P::PST) >> 1) & 1, j >= P::PST, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (quarter == 0) TC_TRACE(half, j, 0);
@@ -635,12 +653,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
             // 32-key chunks of this half that hold at least one key
             const int nch = min(NH / 32, max(0, (min(N, a.Lk - j * N) - half * NH + 31) >> 5));
-            if (nch > 0 && j >= P::PST) {   // the P buffer is free once the MMA that read it has completed
-                const int jp = j - P::PST;
-                ok = mbar_wait(&bar_pv[jp & 1], (jp >> 1) & 1, abort_flag, 13);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
             if (quarter == 0) TC_TRACE(half, j, 1);
             if (nch > 0) {
                 tc_fence_after();
