@@ -524,9 +524,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
     uint64_t* bar_pk = bars;          // [2] packed K rows landed (tx bytes)
     uint64_t* bar_k = bars + 2;       // [2] K operand tile written (128 producers)
-    uint64_t* bar_v = bars + 4;       // [2] V operand tile written (128 producers)
+    uint64_t* bar_v = bars + 4;       // [2] V operand tile and its normaliser tile written (96 producers)
     uint64_t* bar_s = bars + 6;       // [2] S = Q K^T complete (tcgen05.commit): K stage free again
-    uint64_t* bar_p = bars + 8;       // [2] P written, O rescaled (256 softmax threads)
+    uint64_t* bar_p = bars + 8;       // [2] P written (the softmax threads that own real query rows)
     uint64_t* bar_pv = bars + 10;     // [2] O += P V complete (tcgen05.commit): V stage and P buffer free
     uint64_t* bar_o = bars + 12;      // all MMAs complete
     uint64_t* bar_t = bars + 13;      // [4] per-key tables of tile j written (slot j % 4; 128 producers)
