@@ -421,9 +421,9 @@ def run_case(name):
         q = torch.nn.functional.normalize(torch.randn((B, lq, HEADS, HEAD_DIM), generator=g, device=dev), dim=-1) * Q_GAIN
         fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
         nbytes = None
-    else:                     # "quant": 252 MB of fp32 K, per-head INT8, batch-shared groups
+    else:                     # "quant": 252 MB of fp32 K, per-head INT8, batch-shared groups; "quant2": per-dim groups (two passes)
         x = torch.randn((128, 256, 30, 64), generator=g, device=dev)
-        qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=256)
+        qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD" if name == "quant" else "G_SCALE_HEAD_DIM", max_tokens=256)
         fn = lambda: qz.quant(x)
         nbytes = x.numel() * 5
     for _ in range(3):
@@ -444,7 +444,7 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--case", choices=("attn", "quant"), help="run one kernel on a small case and exit (profiling aid)")
+    ap.add_argument("--case", choices=("attn", "quant", "quant2"), help="run one kernel on a small case and exit (profiling aid)")
     args = ap.parse_args()
     if args.case:
         return run_case(args.case)

@@ -410,7 +410,14 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
                 if (!ok[u]) continue;
 #pragma unroll
                 for (int j = 0; j < VPW; ++j)
-                    if (j < n_valid) frange_add<SYM>(acc[uniform ? 0 : j], v[u][j]);
+                    if (j < n_valid) frange_add<SYM>(acc[j], v[u][j]);
+            }
+        }
+        if (uniform) {      // the thread's values share one group: fold them once, here
+#pragma unroll
+            for (int j = 1; j < VPW; ++j) {
+                acc[0].hi = fmaxf(acc[0].hi, acc[j].hi);
+                acc[0].lo = fminf(acc[0].lo, acc[j].lo);
             }
         }
         Range ord[VPW];
@@ -465,9 +472,15 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
             load_vals<T, VPW, VEC>(xcol + ri.xoff, v, n_valid);
 #pragma unroll
             for (int j = 0; j < VPW; ++j)
-                if (j < n_valid) frange_add<SYM>(acc[uniform ? 0 : j], v[j]);
+                if (j < n_valid) frange_add<SYM>(acc[j], v[j]);
         }
         if (uniform) {
+#pragma unroll
+            for (int j = 1; j < VPW; ++j) {
+                acc[0].hi = fmaxf(acc[0].hi, acc[j].hi);
+                acc[0].lo = fminf(acc[0].lo, acc[j].lo);
+                frange_init<SYM>(acc[j]);
+            }
             const long long gid = ok ? group_id(a, b, l, h, d0) : -1;
             const Range mine = frange_ord<SYM>(acc[0]);
             int same;
@@ -504,6 +517,7 @@ template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
     constexpr int UN = TAB_UNROLL;
+    constexpr bool REPL = VPW <= 4;      // replicating shared parameters costs 6 registers per value: only for short words
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     if (cs >= a.H * a.words) return;
     const int h = cs / a.words, w = cs % a.words;
@@ -529,6 +543,10 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
             rg.lo = a.stats[gid * 2 + 1];
             params_from_range(rg, a.bits, SYM, a.eps, scale[j], zp[j]);
             gq[j] = make_group_q(scale[j], zp[j], a.bits);
+        }
+        if (REPL && uniform) {   // one group for all of the thread's values: replicate, so the inner loop never selects
+#pragma unroll
+            for (int j = 1; j < VPW; ++j) gq[j] = gq[0];
         }
     };
     if (!row_dep) fetch(0, 0);
@@ -556,7 +574,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
-                    const GroupQ g = uniform ? gq[0] : gq[j];
+                    const GroupQ g = (REPL || !uniform) ? gq[j] : gq[0];
                     word |= (quant_code<SYM>(v[u][j], g) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
