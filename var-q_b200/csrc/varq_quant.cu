@@ -513,6 +513,26 @@ __global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters
     else             quant_stats_body<T, STORE_BITS, VEC, false>(a, iters, s_fold);
 }
 
+// Between the two passes: one thread per group turns its (max, min) entry into the scale and zero-point that
+// the caller gets back; the apply pass reads them from there instead of redoing the divisions per row.
+__global__ void __launch_bounds__(256) quant_finalize_kernel(QuantArgs a, long long groups) {
+    const long long gid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (gid >= groups) return;
+    long long r = gid;
+    const int g = (int)(r % a.nG); r /= a.nG;
+    const int hh = (int)(r % a.nH); r /= a.nH;
+    const int ll = (int)(r % a.nL);
+    const int bb = (int)(r / a.nL);
+    Range rg;
+    rg.hi = a.stats[gid * 2];
+    rg.lo = a.stats[gid * 2 + 1];
+    float scale, zp;
+    params_from_range(rg, a.bits, a.symmetric != 0, a.eps, scale, zp);
+    const long long pi = bb * a.ps_b + ll * a.ps_r + hh * a.ps_h + (long long)g * a.ps_g;
+    a.scale[pi] = scale;
+    if (!a.symmetric) a.zp[pi] = zp;
+}
+
 template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
@@ -530,19 +550,16 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
     int32_t* ccol = a.codes + h * a.cs_h + w;
 
-    float scale[VPW], zp[VPW];
     GroupQ gq[VPW];
+    const long long p_h = h * a.ps_h;
     auto fetch = [&](int b, int l) {
+        const long long p_row = (a.share_b ? 0 : b) * a.ps_b + (a.share_l ? 0 : l) * a.ps_r + (a.share_h ? 0 : p_h);
 #pragma unroll
         for (int j = 0; j < VPW; ++j) {      // compile-time trip count keeps the per-value parameters in registers
             if (j >= np) break;
             const int d = min(d0 + j, a.D - 1);
-            const long long gid = group_id(a, b, l, h, d);
-            Range rg;
-            rg.hi = a.stats[gid * 2];
-            rg.lo = a.stats[gid * 2 + 1];
-            params_from_range(rg, a.bits, SYM, a.eps, scale[j], zp[j]);
-            gq[j] = make_group_q(scale[j], zp[j], a.bits);
+            const long long pi = p_row + (long long)(d / a.group) * a.ps_g;
+            gq[j] = make_group_q(a.scale[pi], SYM ? 0.0f : a.zp[pi], a.bits);
         }
         if (REPL && uniform) {   // one group for all of the thread's values: replicate, so the inner loop never selects
 #pragma unroll
@@ -579,20 +596,6 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
                 }
             }
             ccol[co[u]] = (int32_t)word;
-            // one writer per group: the member with the lowest shared coordinates
-            const bool first = (a.share_b ? b == 0 : true) && (a.share_l ? l == 0 : true) && (a.share_h ? h == 0 : true);
-            if (first) {
-#pragma unroll
-                for (int j = 0; j < VPW; ++j) {
-                    if (j >= np) break;
-                    const int d = d0 + j;
-                    if (d < a.D && (d % a.group) == 0) {
-                        const long long pi = b * a.ps_b + l * a.ps_r + h * a.ps_h + (long long)(d / a.group) * a.ps_g;
-                        a.scale[pi] = scale[j];
-                        if (!SYM) a.zp[pi] = zp[j];
-                    }
-                }
-            }
         }
     }
 }
@@ -725,15 +728,18 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     const int iters = (int)((R + gy * ty - 1) / (gy * ty));
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
     const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
+    const unsigned fin_blocks = (unsigned)((groups + 255) / 256);
     if (vec) {
         quant_stats_kernel<T, SB, true><<<grid, block, fold, st>>>(a, iters);
+        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);
         quant_apply_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
     } else {
         quant_stats_kernel<T, SB, false><<<grid, block, fold, st>>>(a, iters);
+        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);
         quant_apply_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
     }
     VARQ_CUDA_TRY(cudaGetLastError());
-    count_launches(2);
+    count_launches(3);
     return VARQ_OK;
 }
 
