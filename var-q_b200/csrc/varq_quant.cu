@@ -26,6 +26,7 @@ struct QuantArgs {
     int share_b, share_l, share_h, group;
     int nL, nH, nG;                     // statistics table dims ([nB, nL, nH, nG], 1 where shared)
     uint32_t* stats;                    // [groups][2]: ord(max), ~ord(min)  (zero-initialised)
+    int l_fixed;                        // tables path: the row stride is a multiple of L, so a thread keeps its token index
 };
 
 struct Range { uint32_t hi, lo; };      // hi = max f2ord(x or |x|), lo = max ~f2ord(x)
@@ -384,7 +385,8 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
     const int d0 = w * VPW;
     const int n_valid = min(VPW, a.D - d0);
     const bool uniform = (a.group % VPW) == 0;      // one group per thread-vector
-    const bool row_dep = !(a.share_b && a.share_l); // group depends on the (b, l) row
+    // the group depends on the (b, l) row, unless l is shared or every row of this thread has the same l
+    const bool row_dep = !(a.share_b && (a.share_l || a.l_fixed));
     const unsigned R = (unsigned)a.B * (unsigned)a.L;       // host guarantees < 2^31
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
 
@@ -394,6 +396,7 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
 
     RowIter ri;
     ri.init(a, blockIdx.y * blockDim.y + threadIdx.y, gridDim.y * blockDim.y);
+    const int l0 = (int)ri.l;                       // this thread's token index when it is fixed
     if (!row_dep) {
         // ---- statistics do not depend on the row: accumulate in registers, several loads in flight
         for (int it = 0; it < iters; it += TAB_UNROLL) {
@@ -443,7 +446,7 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
             }
         }
         if (uniform) {
-            const long long gid = col_ok ? group_id(a, 0, 0, h, d0) : -1;
+            const long long gid = col_ok ? group_id(a, 0, l0, h, d0) : -1;
             int same;
             __match_all_sync(__activemask(), gid, &same);
             if (same && __activemask() == 0xffffffffu) {
@@ -459,7 +462,7 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
         } else if (col_ok) {
 #pragma unroll
             for (int j = 0; j < VPW; ++j)
-                if (j < n_valid) stats_flush(a.stats, group_id(a, 0, 0, h, d0 + j), ord[j], SYM);
+                if (j < n_valid) stats_flush(a.stats, group_id(a, 0, l0, h, d0 + j), ord[j], SYM);
         }
         return;
     }
@@ -544,7 +547,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     const int d0 = w * VPW;
     const int n_valid = min(VPW, a.D - d0);
     const bool uniform = (a.group % VPW) == 0;
-    const bool row_dep = !(a.share_b && a.share_l);
+    const bool row_dep = !(a.share_b && (a.share_l || a.l_fixed));
     const unsigned R = (unsigned)a.B * (unsigned)a.L;
     const int np = uniform ? 1 : VPW;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
@@ -566,10 +569,10 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
             for (int j = 1; j < VPW; ++j) gq[j] = gq[0];
         }
     };
-    if (!row_dep) fetch(0, 0);
-
     RowIter ri;
     ri.init(a, blockIdx.y * blockDim.y + threadIdx.y, gridDim.y * blockDim.y);
+    if (!row_dep) fetch(0, (int)ri.l);
+
     for (int it = 0; it < iters; it += UN) {
         float v[UN][VPW];
         unsigned rb[UN], rl[UN];
@@ -716,7 +719,9 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     const int cols = a.H * a.words;
     int tx = 32;
     while (tx < cols && tx < 256) tx <<= 1;
-    const int ty = 256 / tx;
+    // per-token groups shared over the batch keep one row per thread block row (see l_fixed below)
+    const bool per_token = a.share_b && !a.share_l && a.L <= 65535;
+    const int ty = per_token ? 1 : 256 / tx;
     const long long R = (long long)a.B * a.L;
     const int gx = (cols + tx - 1) / tx;
     long long gy = (R + ty - 1) / ty;
@@ -725,6 +730,17 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     if (gy > cap) gy = cap;
     if (gy < 1) gy = 1;
     if (gy > 65535) gy = 65535;
+    // Parameters that depend on the token but not on the sample (per-token groups shared over the batch): with a
+    // row stride of k * L every thread stays on one token, accumulates over the batch in registers and flushes once.
+    a.l_fixed = 0;
+    if (per_token) {
+        long long k = cap * (256 / tx) / a.L;          // thread blocks are tx x 1 here
+        if (k > 65535 / a.L) k = 65535 / a.L;
+        if (k > a.B) k = a.B;
+        if (k < 1) k = 1;
+        gy = (long long)a.L * k;
+        a.l_fixed = 1;
+    }
     const int iters = (int)((R + gy * ty - 1) / (gy * ty));
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
     const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
@@ -790,7 +806,7 @@ extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int
     const int vpw = 32 / store_bits;
     QuantArgs a;
     a.x = x->ptr; a.xs_b = x->stride_b; a.xs_l = x->stride_l; a.xs_h = x->stride_h;
-    a.B = B; a.L = L; a.H = H; a.D = D;
+    a.B = B; a.L = L; a.H = H; a.D = D; a.l_fixed = 0;
     a.bits = bits; a.symmetric = p->zp == nullptr; a.words = (D + vpw - 1) / vpw; a.eps = eps;
     a.codes = (int32_t*)codes->ptr; a.cs_b = codes->stride_b; a.cs_l = codes->stride_l; a.cs_h = codes->stride_h;
     a.scale = p->scale; a.zp = p->zp;
