@@ -1,25 +1,36 @@
 """Benchmark of the KV-cache quantization hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Workload (one "step" = the whole hot path of one generated image batch): the VAR-d16 256px
-configuration -- 16 blocks, 16 heads, head_dim 64, batch 32 with CFG doubling to 64, the ten
-scales 1,2,3,4,5,6,8,10,13,16 (680 tokens), INT8 per-head symmetric KV cache.  For every block
-and every scale the step quantizes+packs the scale's fresh K (fp32, L2-normalised, as the VAR
-attention hands it over) and V (bf16, a strided view into the fused QKV activation) into the
-packed cache and runs attention of the scale's queries over everything cached, writing bf16.
-The surrounding transformer (QKV/MLP GEMMs, sampling, VQVAE) is not part of the path and not
-run.  Inputs are seeded synthetic tensors of those shapes; the same ten (q, k, v) triples feed
-all 16 blocks, each block owning its caches.
+One "step" is the whole hot path of one generated image batch of a model configuration: for every
+transformer block and every scale of the schedule, quantize+pack the scale's fresh K and V into the
+block's packed cache and run attention of the scale's queries over everything cached.  The
+surrounding transformer (QKV / MLP GEMMs, sampling, image tokenizer) is not part of the path and is
+not run, so the metric is hot-path images/s.  Inputs are seeded synthetic tensors of the model's
+shapes and dtypes (there are no checkpoints, labels or prompts on the box); the same per-scale
+(q, k, v) feed every block, each block owning its caches.
 
-With --gpus N (launched through torch.distributed.run) every rank runs the same batch-32 job on
-its own GPU -- batch-sharded replicas, no collective on the path -- and the value is the sum
-over ranks divided by the slowest rank's device time (weak scaling).
+Workloads (BASELINE.json `configs`):
+  infinity_2b  (default, the largest single-GPU configuration) Infinity-2B-like: 32 blocks, 16 heads,
+               head_dim 128, 13 scales to 10 521 tokens, batch 8 (+CFG = 16), layout BHLc, K INT4 / V INT2 in
+               asymmetric groups of 32 along head_dim;
+  var_d30      VAR-d30: 30 blocks, 30 heads, head_dim 64, 10 scales to 2 240 tokens, batch 64 (+CFG = 128),
+               layout BLHc, K per-dim asymmetric INT4, V per-(token, head) asymmetric INT4 (group 64);
+  var_d16      VAR-d16: 16 blocks, 16 heads, head_dim 64, 10 scales to 680 tokens, batch 32 (+CFG = 64),
+               INT8 per-(token, head) symmetric.
+The headline line is on --workload; the two others are run for a few steps and reported under
+`other_workloads` (N = 1 only).
 
---impl reference times the CPU restatement of the reference algorithm (oracle/) on the host
-cores on a bounded sample (whole blocks of the same workload) and scales to the full step.
+With --gpus N (launched through torch.distributed.run) every rank runs the same job on its own GPU:
+the global batch of N x images is cut by VAR_Q.sharding.shard_images, no collective is on the path,
+and the value is all ranks' images over the slowest rank's device time (weak scaling).
+
+--impl reference times the CPU restatement of the reference algorithm (oracle/) on the host cores; a
+step there is a bounded sample of the same workload (one block on a batch subset), and the value is
+scaled by the fraction of a full step the sample covers.
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -34,64 +45,102 @@ for p in (ROOT, os.path.join(ROOT, "var-q_b200")):
 
 import torch  # noqa: E402
 
-PATCH_NUMS = (1, 2, 3, 4, 5, 6, 8, 10, 13, 16)
-DEPTH, HEADS, HEAD_DIM, IMAGES = 16, 16, 64, 32
-B2 = 2 * IMAGES
-STEPS_L = tuple(p * p for p in PATCH_NUMS)
-L_TOTAL = sum(STEPS_L)
-Q_GAIN = 4.0            # exp(scale_mul_1H11) at initialisation (VAR/models/basic_var.py:86)
-WORKLOAD = "VAR-d16 256px KV hot path: 16 blocks x 10 scales x (quantize+pack K, V; attention over packed cache), B=32 (+CFG=64), H=16, c=64, INT8 per-head symmetric"
+Q_GAIN = 4.0            # exp(scale_mul) at initialisation (VAR/models/basic_var.py:86; Infinity/infinity/models/basic.py:223-230)
+
+WORKLOADS = {
+    "var_d16": dict(
+        depth=16, heads=16, head_dim=64, images=32, fmt="BLHc",
+        steps_l=tuple(p * p for p in (1, 2, 3, 4, 5, 6, 8, 10, 13, 16)),
+        k=(8, "G_TOKEN_HEAD", {}), v=(8, "G_TOKEN_HEAD", {}), cpu_b2=16, cpu_heads=16,
+        desc="VAR-d16 256px KV hot path: 16 blocks x 10 scales x (quantize+pack K, V; attention over packed cache), "
+             "B=32 (+CFG=64), H=16, c=64, INT8 per-head symmetric"),
+    "var_d30": dict(
+        depth=30, heads=30, head_dim=64, images=64, fmt="BLHc",
+        steps_l=tuple(p * p for p in (1, 2, 3, 4, 6, 9, 13, 18, 24, 32)),
+        k=(4, "G_SCALE_HEAD_DIM", dict(symmetric=False)), v=(4, "G_TOKEN_HEAD", dict(symmetric=False, group_size=64)), cpu_b2=8, cpu_heads=8,
+        desc="VAR-d30 512px-schedule KV hot path: 30 blocks x 10 scales (2240 tokens), B=64 (+CFG=128), H=30, c=64, "
+             "K per-dim asymmetric INT4, V per-head asymmetric INT4 group 64"),
+    "infinity_2b": dict(
+        depth=32, heads=16, head_dim=128, images=8, fmt="BHLc",
+        steps_l=tuple(p * p for p in (1, 2, 4, 6, 8, 12, 16, 20, 24, 32, 40, 48, 64)),
+        k=(4, "G_TOKEN_HEAD", dict(symmetric=False, group_size=32)), v=(2, "G_TOKEN_HEAD", dict(symmetric=False, group_size=32)),
+        cpu_b2=2, cpu_heads=4,
+        desc="Infinity-2B-like 1024px KV hot path: 32 blocks x 13 scales (10521 tokens), B=8 (+CFG=16), H=16, c=128, "
+             "group-wise asymmetric INT4 K / INT2 V, group 32"),
+}
+DEFAULT_WORKLOAD = "infinity_2b"
+METRIC = "kv_hot_path_images_per_sec"
 
 
 # --------------------------------------------------------------------------- inputs
-def make_inputs(device, seed=0, pin_host=False):
-    """Per scale: q fp32 [B2,l,H,c] (unit rows x gain), k fp32 (unit rows), v bf16 strided view."""
-    g = torch.Generator(device="cpu").manual_seed(seed)
+def item_shape(w, b2, l):
+    return (b2, l, w["heads"], w["head_dim"]) if w["fmt"] == "BLHc" else (b2, w["heads"], l, w["head_dim"])
+
+
+def make_inputs(w, device, seed, b2=None, heads=None):
+    """Per scale: q fp32 (unit rows x gain), k fp32 (unit rows), v bf16.  In the BLHc (VAR) layout v is the strided
+    third of a fused [B, l, 3, H, c] activation, as the hook receives it; in BHLc (Infinity) all three are contiguous."""
+    b2 = b2 or 2 * w["images"]
+    g = torch.Generator(device=device).manual_seed(seed)
     out = []
-    for l in STEPS_L:
-        qkv = torch.randn((B2, l, 3, HEADS, HEAD_DIM), generator=g, dtype=torch.float32)
-        qkv[..., :4] *= 6.0                      # a few large channels, as K/V activations show
-        q = torch.nn.functional.normalize(qkv[:, :, 0], dim=-1) * Q_GAIN
-        k = torch.nn.functional.normalize(qkv[:, :, 1], dim=-1)
-        rec = {"q": q.contiguous(), "k": k.contiguous(), "qkv16": qkv.to(torch.bfloat16).contiguous()}
-        rec["v16"] = rec["qkv16"][:, :, 2].contiguous()     # the V third alone: what the end-to-end leg uploads
-        if pin_host:
-            rec = {n: t.pin_memory() for n, t in rec.items()}
-        out.append(rec)
-    if device is None:
-        return out
-    dev = []
-    for rec in out:
-        qkv16 = rec["qkv16"].to(device)
-        dev.append({"q": rec["q"].to(device), "k": rec["k"].to(device), "qkv16": qkv16, "v": qkv16.unbind(dim=2)[2]})
-    return dev, out
+    for l in w["steps_l"]:
+        H, c = heads or w["heads"], w["head_dim"]
+        if w["fmt"] == "BLHc":
+            qkv = torch.randn((b2, l, 3, H, c), generator=g, dtype=torch.float32, device=device)
+            qkv[..., :4] *= 6.0                      # a few large channels, as K/V activations show
+            q = torch.nn.functional.normalize(qkv[:, :, 0], dim=-1) * Q_GAIN
+            k = torch.nn.functional.normalize(qkv[:, :, 1], dim=-1)
+            qkv16 = qkv.to(torch.bfloat16)
+            del qkv
+            out.append({"q": q.contiguous(), "k": k.contiguous(), "v": qkv16.unbind(dim=2)[2], "_qkv16": qkv16})
+        else:
+            x = torch.randn((3, b2, H, l, c), generator=g, dtype=torch.float32, device=device)
+            x[..., :4] *= 6.0
+            q = torch.nn.functional.normalize(x[0], dim=-1) * Q_GAIN
+            k = torch.nn.functional.normalize(x[1], dim=-1)
+            v = x[2].to(torch.bfloat16)
+            del x
+            out.append({"q": q.contiguous(), "k": k.contiguous(), "v": v.contiguous()})
+    return out
 
 
-def algorithmic_bytes_attn(lq, lk):
-    """Packed K+V codes, their per-(token, head) scales, Q in and O out, for one launch."""
-    kv = B2 * HEADS * lk * HEAD_DIM * (8 + 8) // 8
-    params = 2 * lk * HEADS * 4
-    return kv + params + B2 * HEADS * lq * HEAD_DIM * (4 + 2)
+def attn_flops(w, b2, lq, lk):
+    return 4 * b2 * w["heads"] * lq * lk * w["head_dim"]
 
 
-def algorithmic_bytes_quant(l, in_bytes):
-    n = B2 * l * HEADS * HEAD_DIM
-    return n * in_bytes + n + l * HEADS * 4
+def attn_bytes(w, b2, lq, lk, q_bytes=4, o_bytes=2):
+    """Packed K+V codes, their scales / zero-points, Q in and O out of one attention launch."""
+    H, c = w["heads"], w["head_dim"]
+    total = 0
+    for bits, mode, kw in (w["k"], w["v"]):
+        total += b2 * H * lk * c * bits // 8
+        k_par = 1 if kw.get("symmetric", True) else 2
+        if mode == "G_TOKEN_HEAD":
+            total += lk * H * (c // kw.get("group_size", c) if kw.get("group_size") else 1) * 4 * k_par
+        elif mode == "G_SCALE_HEAD_DIM":
+            total += len(w["steps_l"]) * H * c * 4 * k_par
+    return total + b2 * H * lq * c * (q_bytes + o_bytes)
+
+
+def quant_bytes(n_elems, in_bytes, bits, groups, symmetric):
+    return n_elems * in_bytes + n_elems * bits // 8 + groups * 4 * (1 if symmetric else 2)
 
 
 # --------------------------------------------------------------------------- GPU arm
-def new_quantizers():
+def new_quantizers(w):
     from VAR_Q.quant import VAR_Q
-    mk = lambda blk: VAR_Q(quant_bits=8, qkv_format="BLHc", quant_method="G_TOKEN_HEAD", blk_idx=blk, max_tokens=L_TOTAL)
-    return [(mk(b), mk(b)) for b in range(DEPTH)]
+    total = sum(w["steps_l"])
+    (kb, km, kkw), (vb, vm, vkw) = w["k"], w["v"]
+    return [(VAR_Q(kb, w["fmt"], km, blk_idx=b, max_tokens=total, **kkw), VAR_Q(vb, w["fmt"], vm, blk_idx=b, max_tokens=total, **vkw))
+            for b in range(w["depth"])]
 
 
-def hot_path_step(inputs, probe=None):
-    """One image batch through the path.  `probe(kind, si)` may return (start, end) events to
-    record around a call; it is used to time single launches without perturbing the rest."""
+def hot_path_step(w, inputs, probe=None, keep=None):
+    """One image batch through the path.  `probe(kind, si)` may return (start, end) events to record around a call.
+    `keep` = (block, scale): the attention output of that call is returned for a spot check against the oracle."""
     from VAR_Q.attention import attend_cached
-    out = None
-    for kq, vq in new_quantizers():
+    kept = None
+    for bi, (kq, vq) in enumerate(new_quantizers(w)):
         for si, rec in enumerate(inputs):
             ev = probe("quant_k", si) if probe else None
             if ev: ev[0].record()
@@ -105,35 +154,35 @@ def hot_path_step(inputs, probe=None):
             if ev: ev[0].record()
             out = attend_cached(rec["q"], kq, vq, 1.0, out_dtype=torch.bfloat16)
             if ev: ev[1].record()
-    return out
+            if keep == (bi, si):
+                kept = out
+    return kept
 
 
-def e2e_step(host_inputs, device, dev_bufs, host_out, side=None):
-    """Same path through the public API with HOST buffers: every call's inputs (q and k in fp32, v in
-    bf16) are copied from pinned host memory and its result is copied back, inside the timed region.  The copies run
-    on two side streams (`side` = (h2d_stream, d2h_stream)) so that the upload of the next call,
-    this call's kernels and the download of the previous result overlap; every buffer reuse is
-    ordered by events, and the calling stream joins both side streams before returning."""
+def e2e_step(w, host_inputs, device, dev_bufs, host_out, side):
+    """Same path through the public API with HOST buffers: every call's inputs (q and k in fp32, v in bf16) are copied
+    from pinned host memory and its result is copied back, inside the timed region.  The copies run on two side
+    streams so that the upload of the next call, this call's kernels and the download of the previous result overlap;
+    every buffer reuse is ordered by events, and the calling stream joins both side streams before returning."""
     from VAR_Q.attention import attend_cached
     main = torch.cuda.current_stream(device)
-    up, down = side if side is not None else (main, main)
+    up, down = side
     h2d = d2h = 0
     in_free = [None] * len(host_inputs)          # recorded on `main` once a scale's device inputs have been consumed
-    for kq, vq in new_quantizers():
+    for kq, vq in new_quantizers(w):
         for si, rec in enumerate(host_inputs):
             buf = dev_bufs[si]
             with torch.cuda.stream(up):
                 if in_free[si] is not None:
                     up.wait_event(in_free[si])
-                buf["q"].copy_(rec["q"], non_blocking=True)
-                buf["k"].copy_(rec["k"], non_blocking=True)
-                buf["v16"].copy_(rec["v16"], non_blocking=True)
+                for name in ("q", "k", "v"):
+                    buf[name].copy_(rec[name], non_blocking=True)
+                    h2d += rec[name].numel() * rec[name].element_size()
                 ready = torch.cuda.Event()
                 ready.record(up)
-            h2d += rec["q"].numel() * 4 + rec["k"].numel() * 4 + rec["v16"].numel() * 2
             main.wait_event(ready)
             kq.append(buf["k"])
-            vq.append(buf["v16"])
+            vq.append(buf["v"])
             out = attend_cached(buf["q"], kq, vq, 1.0, out_dtype=torch.bfloat16)
             in_free[si] = torch.cuda.Event()
             in_free[si].record(main)
@@ -186,16 +235,337 @@ class ClockSampler(threading.Thread):
 
 
 def load_peaks():
+    """Measured peaks of this pool's B200s: copy bandwidth, bf16 GEMM as a burst (a kernel timed alone) and sustained
+    (a kernel timed inside a long step)."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return {"hbm_gbs": p["hbm_gbs"], "tflops": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops_burst": p["bf16_tflops"],
+                "tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def time_launches(fn, reps=10, warm=3):
+    """Mean device time of `fn` over `reps` back-to-back calls on the current stream (CUDA events)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def roof_entry(name, case, ms, peaks, nbytes=None, flops=None, kernels=None):
+    """Roofline record of a kernel timed alone: tensor-bound when its flops per byte exceed the burst ridge."""
+    ridge = peaks["tflops_burst"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+    tensor = flops is not None and nbytes and flops / nbytes > ridge
+    rec = {"kernel": name, "case": case, "launch_ms": ms, "algorithmic_bytes": nbytes, "algorithmic_flops": flops,
+           "peak_source": peaks["source"], "peak_kind": "burst (kernel timed alone)"}
+    if kernels:
+        rec["launches_per_call"] = kernels
+    if tensor:
+        ach = flops / (ms * 1e-3) / 1e12
+        rec.update({"bound": "tensor", "achieved": ach, "peak": peaks["tflops_burst"], "unit": "TFLOP/s", "frac": ach / peaks["tflops_burst"]})
+    else:
+        ach = nbytes / (ms * 1e-3) / 1e9
+        rec.update({"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]})
+    return rec
+
+
+def kernel_rooflines(device, peaks):
+    """One record per kernel class, each on a shape larger than L2, timed alone with CUDA events."""
+    from VAR_Q.attention import attend_cached
+    from VAR_Q.quant import VAR_Q
+    from VAR_Q import _cabi
+    lib = _cabi.lib()
+    g = torch.Generator(device=device).manual_seed(7)
+    recs = []
+
+    def counted(fn):
+        n0 = lib.varq_launch_count()
+        fn()
+        return lib.varq_launch_count() - n0
+
+    # ---- quantize + pack on the VAR-d30 last-step tensor [128, 1024, 30, 64] (fp32: 1.0 GB)
+    x = torch.randn((128, 1024, 30, 64), generator=g, device=device)
+    n = x.numel()
+    for name, bits, mode, kw, groups in (
+            ("quantize+pack, single pass (per-head INT8)", 8, "G_TOKEN_HEAD", {}, 1024 * 30),
+            ("quantize+pack, single pass (per-head asymmetric INT4)", 4, "G_TOKEN_HEAD", dict(symmetric=False), 1024 * 30),
+            ("quantize+pack, two passes (per-dim INT8, the reference's shipped mode)", 8, "G_SCALE_HEAD_DIM", {}, 30 * 64),
+            ("quantize+pack, two passes (per-dim asymmetric INT4)", 4, "G_SCALE_HEAD_DIM", dict(symmetric=False), 30 * 64)):
+        qz = VAR_Q(bits, "BLHc", mode, max_tokens=1024, **kw)
+        fn = lambda: qz.quant(x)
+        ms = time_launches(fn, reps=5)
+        recs.append(roof_entry(name, "fp32 [128,1024,30,64] BLHc", ms, peaks,
+                               nbytes=quant_bytes(n, 4, bits, groups, kw.get("symmetric", True)), kernels=counted(fn)))
+    x16 = x.to(torch.bfloat16)
+    qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=1024)
+    fn = lambda: qz.quant(x16)
+    recs.append(roof_entry("quantize+pack, single pass (per-head INT8)", "bf16 [128,1024,30,64] BLHc", time_launches(fn, reps=5), peaks,
+                           nbytes=quant_bytes(n, 2, 8, 1024 * 30, True), kernels=counted(fn)))
+    # ---- unpack + dequant of the same cache to fp32
+    qz.cache()
+    fn = lambda: qz.dequant_all()
+    recs.append(roof_entry("unpack+dequant to fp32 (per-head INT8)", "[128,1024,30,64]", time_launches(fn, reps=5), peaks,
+                           nbytes=n + 1024 * 30 * 4 + n * 4, kernels=counted(fn)))
+    del x, x16, qz
+
+    # ---- Infinity-2B last step [16,16,4096,128]: group-32 asymmetric INT4 of fp32 K, INT2 of bf16 V
+    xk = torch.randn((16, 16, 4096, 128), generator=g, device=device)
+    n = xk.numel()
+    for name, bits, x_in, ib in (("quantize+pack, single pass (group-32 asymmetric INT4)", 4, xk, 4),
+                                 ("quantize+pack, single pass (group-32 asymmetric INT2)", 2, xk.to(torch.bfloat16), 2)):
+        qz = VAR_Q(bits, "BHLc", "G_TOKEN_HEAD", max_tokens=4096, symmetric=False, group_size=32)
+        fn = lambda: qz.quant(x_in)
+        recs.append(roof_entry(name, f"{'fp32' if ib == 4 else 'bf16'} [16,16,4096,128] BHLc", time_launches(fn, reps=5), peaks,
+                               nbytes=quant_bytes(n, ib, bits, 16 * 4096 * 4, False), kernels=counted(fn)))
+    del xk, qz
+
+    # ---- attention over a packed cache
+    def attn_case(name, B, H, D, lq, lk, k_args, v_args, q_dtype, fmt="BHLc", reps=5):
+        (kb, km, kkw), (vb, vm, vkw) = k_args, v_args
+        kq, vq = VAR_Q(kb, fmt, km, max_tokens=lk, **kkw), VAR_Q(vb, fmt, vm, max_tokens=lk, **vkw)
+        shape = (B, H, lk, D) if fmt == "BHLc" else (B, lk, H, D)
+        k = torch.nn.functional.normalize(torch.randn(shape, generator=g, device=device), dim=-1)
+        kq.append(k)
+        del k
+        vq.append(torch.randn(shape, generator=g, device=device).to(torch.bfloat16))
+        qshape = (B, H, lq, D) if fmt == "BHLc" else (B, lq, H, D)
+        q = (torch.nn.functional.normalize(torch.randn(qshape, generator=g, device=device), dim=-1) * Q_GAIN).to(q_dtype)
+        fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
+        ms = time_launches(fn, reps=reps)
+        w = dict(heads=H, head_dim=D, k=k_args, v=v_args, steps_l=(lk,))
+        qb = 4 if q_dtype == torch.float32 else 2
+        recs.append(roof_entry(name, f"B{B} H{H} Lq{lq} Lk{lk} c{D} K{kb}b V{vb}b q {str(q_dtype).split('.')[-1]}", ms, peaks,
+                               nbytes=attn_bytes(w, B, lq, lk, q_bytes=qb), flops=attn_flops(w, B, lq, lk), kernels=counted(fn)))
+
+    ph8 = (8, "G_TOKEN_HEAD", {})
+    for bits in (8, 4, 2):
+        a = (bits, "G_TOKEN_HEAD", {})
+        attn_case(f"attention, streaming CUDA-core kernel (per-head INT{bits})", 64, 16, 128, 1, 10521, a, a, torch.bfloat16)
+    g32 = lambda b: (b, "G_TOKEN_HEAD", dict(symmetric=False, group_size=32))
+    attn_case("attention, streaming CUDA-core kernel (group-32 INT4 K / INT2 V)", 64, 16, 128, 1, 10521, g32(4), g32(2), torch.bfloat16)
+    attn_case("attention, streaming CUDA-core kernel, 16 queries (per-head INT8)", 64, 16, 128, 16, 10521, ph8, ph8, torch.bfloat16)
+    attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 64, 16, 64, 256, 680, ph8, ph8, torch.float32, fmt="BLHc", reps=20)
+    attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 64, 16, 64, 1024, 2240, ph8, ph8, torch.bfloat16, fmt="BLHc")
+    attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 16, 16, 128, 4096, 10521, ph8, ph8, torch.bfloat16)
+    attn_case("attention, tensor-core kernel, per-dim K (asymmetric INT4 K per-dim, V per-head)", 64, 16, 64, 1024, 2240,
+              (4, "G_SCALE_HEAD_DIM", dict(symmetric=False)), (4, "G_TOKEN_HEAD", dict(symmetric=False)), torch.float32, fmt="BLHc")
+    attn_case("attention, tensor-core kernel, group-wise K and V (INT4 K / INT2 V, group 32)", 16, 16, 128, 4096, 10521, g32(4), g32(2), torch.float32)
+    return recs
+
+
+def c5_sweep(device, world, rank, dist):
+    """The isolated dequant-attention sweep of BASELINE.json configs[4]: Q bf16 [64, 16, Lq, D] against 10 521 packed
+    tokens, batch sharded across the ranks.  Returns rows (D, bits, grouping, Lq, ms, TFLOP/s or GB/s)."""
+    from VAR_Q.attention import attend_cached
+    from VAR_Q.quant import VAR_Q
+    from VAR_Q.sharding import shard_images
+    b0, b1 = shard_images(64, world, rank)
+    B, H, lk = b1 - b0, 16, 10521
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    rows, times = [], []
+    for D in (64, 128):
+        for bits in (8, 4, 2):
+            for grouped in (False, True):
+                kw = dict(symmetric=False, group_size=32) if grouped else {}
+                kq, vq = VAR_Q(bits, "BHLc", "G_TOKEN_HEAD", max_tokens=lk, **kw), VAR_Q(bits, "BHLc", "G_TOKEN_HEAD", max_tokens=lk, **kw)
+                k = torch.randn((B, H, lk, D), generator=g, device=device)
+                k[..., :4] *= 20.0
+                kq.append(k)
+                del k
+                vq.append(torch.randn((B, H, lk, D), generator=g, device=device).to(torch.bfloat16))
+                for lq in (1, 16, 256, 1024, 4096):
+                    q = torch.randn((B, H, lq, D), generator=g, device=device).to(torch.bfloat16)
+                    fn = lambda: attend_cached(q, kq, vq, 1.0 / D ** 0.5, out_dtype=torch.bfloat16)
+                    times.append(time_launches(fn, reps=3, warm=1))
+                    rows.append([D, bits, "group32" if grouped else "per_head", lq])
+                del kq, vq
+    t = torch.tensor(times, device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = []
+    for (D, bits, grp, lq), ms in zip(rows, t.tolist()):
+        flops = 4 * 64 * H * lq * lk * D
+        kv_bytes = 64 * H * lk * D * 2 * bits // 8
+        out.append({"D": D, "bits": bits, "grouping": grp, "Lq": lq, "ms": round(ms, 4),
+                    "TFLOP/s": round(flops / ms / 1e9, 1), "packed_KV_GB/s": round(kv_bytes / ms / 1e6, 1)})
+    return out
+
+
+def gpu_eager_baseline(w, device, inputs):
+    """The reference's algorithm as eager torch ops on this GPU, for one block (informational): symmetric abs-max
+    quantize, shift-and-or packing, torch.cat growth of cache and scales, whole-cache unpack + dequant to fp32
+    at every step, cast and scaled_dot_product_attention.  Groupings and zero-points of the workload are kept."""
+    fmt, c = w["fmt"], w["head_dim"]
+    ld = 1 if fmt == "BLHc" else 2
+
+    def quant(x, bits, mode, kw):
+        x = x.float()
+        sym, gs = kw.get("symmetric", True), kw.get("group_size")
+        xs = x.unflatten(-1, (c // gs, gs)) if gs and gs != c else x
+        if mode == "G_TOKEN_HEAD":
+            dims = (0, xs.dim() - 1)
+        else:                                   # G_SCALE_HEAD_DIM
+            dims = (0, ld)
+        lo, hi = -(1 << (bits - 1)), (1 << (bits - 1)) - 1
+        if sym:
+            s = (xs.abs().amax(dims, keepdim=True) / float(hi)).clamp_min(1e-12)
+            z = None
+            qv = torch.round(xs / s).clamp(lo, hi)
+        else:
+            mn, mx = xs.amin(dims, keepdim=True), xs.amax(dims, keepdim=True)
+            s = ((mx - mn) / float((1 << bits) - 1)).clamp_min(1e-12)
+            z = torch.round(lo - mn / s)
+            qv = (torch.round(xs / s) + z).clamp(lo, hi)
+        qv = qv.to(torch.int8).reshape(x.shape)
+        per = 32 // bits
+        u = (qv.to(torch.int32) & ((1 << bits) - 1)).unflatten(-1, (c // per, per))
+        words = (u << (torch.arange(per, device=x.device, dtype=torch.int32) * bits)).sum(-1, dtype=torch.int32)
+        expand = lambda p: None if p is None else p.expand(*[x.size(i) if i == ld else -1 for i in range(p.dim())]) if p.size(ld) == 1 else p
+        return words, expand(s), expand(z), (bits, per, xs.shape[-1] if xs.dim() == 5 else None)
+
+    def dequant(words, s, z, meta):
+        bits, per, gs = meta
+        sh = torch.arange(per, device=words.device, dtype=torch.int32) * bits
+        u = (words.unsqueeze(-1) >> sh) & ((1 << bits) - 1)
+        qv = torch.where(u >= (1 << (bits - 1)), u - (1 << bits), u).flatten(-2).to(torch.int8).float()
+        if gs:
+            qv = qv.unflatten(-1, (c // gs, gs))
+        if z is not None:
+            qv = qv - z
+        out = qv * s
+        return out.flatten(-2) if gs else out
+
+    def block():
+        cache = {}
+        for rec in inputs:
+            kv = []
+            for name, (bits, mode, kw) in (("k", w["k"]), ("v", w["v"])):
+                words, s, z, meta = quant(rec[name], bits, mode, kw)
+                if name in cache:
+                    cw, cs, cz = cache[name]
+                    words, s = torch.cat([cw, words], ld), torch.cat([cs, s], ld)
+                    z = None if z is None else torch.cat([cz, z], ld)
+                cache[name] = (words, s, z)
+                kv.append(dequant(words, s, z, meta).to(torch.bfloat16))
+            q, k, v = rec["q"].to(torch.bfloat16), kv[0], kv[1]
+            if fmt == "BLHc":
+                q, k, v = (t.transpose(1, 2) for t in (q, k, v))
+            out = torch.nn.functional.scaled_dot_product_attention(q, k, v, scale=1.0)
+        return out
+
+    block()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    block()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    return {"value": w["images"] / (ms * 1e-3 * w["depth"]), "unit": "images/s", "ms_per_block": ms,
+            "what": "reference algorithm as eager torch ops + SDPA (bf16) on this GPU, one block timed and scaled by the depth; informational"}
+
+
+def load_traffic(kernel_key):
+    """DRAM bytes per unit for a kernel from the ncu capture recorded in profiles/ncu_traffic.json, valid only while
+    the kernel's source file is the one the capture was taken on."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if not os.path.exists(path):
+        return None, "no ncu capture recorded"
+    rec = json.load(open(path)).get(kernel_key)
+    if not rec:
+        return None, f"no ncu capture recorded for {kernel_key}"
+    src = os.path.join(ROOT, rec["source"])
+    sha = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16] if os.path.exists(src) else None
+    if sha != rec["source_sha256_16"]:
+        return None, f"ncu capture in {rec['summary']} predates the current {rec['source']}"
+    return rec, f"ncu capture summarised in {rec['summary']} (same {rec['source']}), scaled by {rec['unit']}"
+
+
+def run_workload(w, device, args, lib, barrier, steps, warmup, want_probe=True, graph_mode=True):
+    """Warm up, (optionally) capture one step in a CUDA graph, time `steps` steps with CUDA events.  Returns a dict."""
+    inputs = make_inputs(w, device, seed=int(os.environ.get("RANK", "0")))
+    tot = {}
+
+    def probe_all(kind, si):
+        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        tot.setdefault((kind, si), []).append(ev)
+        return ev
+    n_warm = max(warmup, 3)
+    for wi in range(n_warm):
+        hot_path_step(w, inputs, probe_all if (want_probe and wi == n_warm - 1) else None)
+    torch.cuda.synchronize()
+    share = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in tot.items()}
+
+    graph, launches_per_step, kept = None, None, None
+    keep = (w["depth"] - 1, 3)
+    if graph_mode:
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            hot_path_step(w, inputs)                      # allocator warm-up on a side stream
+        torch.cuda.current_stream(device).wait_stream(side)
+        torch.cuda.synchronize()
+        n0 = lib.varq_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            kept = hot_path_step(w, inputs, keep=keep)
+        launches_per_step = lib.varq_launch_count() - n0
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(device.index or 0)
+    barrier()
+    sampler.start()
+    n0 = lib.varq_launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            kept = hot_path_step(w, inputs, keep=keep)
+    t1.record()
+    barrier()
+    launches = launches_per_step * steps if graph is not None else lib.varq_launch_count() - n0
+    clocks = sampler.stop()
+    return {"ms": t0.elapsed_time(t1), "launches": int(launches), "clocks": clocks, "share": share, "inputs": inputs,
+            "kept": kept, "keep": keep, "graph": graph is not None}
+
+
+def oracle_spot_check(w, res, rank):
+    """Attention output of scale 3 of the last block, from the timed run, against the CPU oracle (all blocks see the
+    same inputs, so block 0 of the oracle stands for the last one).  Returns (max-abs error, relative L2)."""
+    from oracle import varq_oracle as O
+    (kb, km, kkw), (vb, vm, vkw) = w["k"], w["v"]
+    kr, vr = O.OracleVARQ(kb, w["fmt"], km, **kkw), O.OracleVARQ(vb, w["fmt"], vm, **vkw)
+    si_keep = res["keep"][1]
+    ref = None
+    for si in range(si_keep + 1):
+        rec = res["inputs"][si]
+        kd, vd = kr.use_var_q(rec["k"].cpu()), vr.use_var_q(rec["v"].cpu())
+        if si == si_keep:
+            ref = O.attention(rec["q"].cpu(), kd, vd, w["fmt"], 1.0)
+    if w["fmt"] == "BHLc":
+        ref = ref.transpose(1, 2)
+    out = res["kept"].float().cpu()
+    err = (out - ref).abs().max().item()
+    rel = ((out - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+    return err, rel
 
 
 def run_ours(args):
     import torch.distributed as dist
     from VAR_Q import _cabi
+    from VAR_Q.attention import attend_cached
+    from VAR_Q.sharding import aggregate_throughput, shard_images
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -204,68 +574,30 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     lib = _cabi.lib()
-    inputs, host_inputs = make_inputs(device, seed=rank, pin_host=True)
+    w = WORKLOADS[args.workload]
+    images = w["images"]
+    # weak scaling: the global batch of world x images is cut in whole images (a CFG pair stays on one GPU)
+    b0, b1 = shard_images(images * world, world, rank)
+    assert b1 - b0 == images
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up; the first warm-up step is probed to find the kernel that dominates
-    tot = {}
-    def probe_all(kind, si):
-        ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-        tot.setdefault((kind, si), []).append(ev)
-        return ev
-    n_warm = max(args.warmup, 3)
-    for w in range(n_warm):
-        hot_path_step(inputs, probe_all if w == n_warm - 1 else None)   # the first steps pay one-off set-up costs
-    torch.cuda.synchronize()
-    share = {k: sum(a.elapsed_time(b) for a, b in v) for k, v in tot.items()}
+    res = run_workload(w, device, args, lib, barrier, args.steps, args.warmup, graph_mode=not args.no_graph)
+    ms, inputs, share = res["ms"], res["inputs"], res["share"]
+    status = _cabi.device_status()
+    if status != 0:
+        raise SystemExit(f"bench.py: a kernel wait expired during the timed region (code {status}); the timing is void")
+    spot_err, spot_rel = oracle_spot_check(w, res, rank)
+    if not (spot_err <= 2e-2 and spot_rel <= 1e-2):      # bf16 output: rounding of 2^-9 relative
+        raise SystemExit(f"bench.py: the timed step's output differs from the oracle (max-abs {spot_err:.3e}, rel-L2 {spot_rel:.3e})")
+
+    # ---- the dominant launch class alone: back-to-back launches on the state it sees in the step
     top = max(share, key=share.get)
-
-    # ---- the step's launches are static, so they are captured once in a CUDA graph and replayed
-    graph, launches_per_step = None, None
-    if not args.no_graph:
-        n0 = lib.varq_launch_count()
-        side = torch.cuda.Stream(device)
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            hot_path_step(inputs)                      # allocator warm-up on the capture stream
-        torch.cuda.current_stream(device).wait_stream(side)
-        torch.cuda.synchronize()
-        n0 = lib.varq_launch_count()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            graph_out = hot_path_step(inputs)
-        launches_per_step = lib.varq_launch_count() - n0
-        for _ in range(2):
-            graph.replay()
-        torch.cuda.synchronize()
-
-    # ---- timed region: K steps, events on the launching stream, clocks sampled alongside
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    n0 = lib.varq_launch_count()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
-            hot_path_step(inputs)
-    t1.record()
-    barrier()
-    launches = launches_per_step * args.steps if graph is not None else lib.varq_launch_count() - n0
-    clocks = sampler.stop()
-    ms = t0.elapsed_time(t1)
-
-    # ---- the dominant kernel alone: back-to-back launches on the state it sees in the step, so that
-    # the CUDA events measure the kernel and not the Python between launches
-    from VAR_Q.attention import attend_cached
     kind, si = top
-    kq, vq = new_quantizers()[0]
+    kq, vq = new_quantizers(w)[0]
     for rec in inputs[:si]:
         kq.append(rec["k"]); vq.append(rec["v"])
     rec = inputs[si]
@@ -276,106 +608,174 @@ def run_ours(args):
         launch = lambda: kq.quant(rec["k"])          # re-quantizes the pending step in place
     else:
         launch = lambda: vq.quant(rec["v"])
-    reps = 20
-    for _ in range(3):
-        launch()
-    torch.cuda.synchronize()
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k0.record()
-    for _ in range(reps):
-        launch()
-    k1.record()
-    torch.cuda.synchronize()
-    top_ms = k0.elapsed_time(k1) / reps
+    top_ms = time_launches(launch, reps=10 if kind == "attn" else 20)
+    n0 = lib.varq_launch_count(); launch(); top_launches = lib.varq_launch_count() - n0
+    del kq, vq
+
+    # ---- the same step launched from Python (no CUDA graph), a few steps
+    eager_ms = None
+    if not args.no_graph and not args.quick:
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(2):
+            hot_path_step(w, inputs)
+        e1.record()
+        torch.cuda.synchronize()
+        eager_ms = e0.elapsed_time(e1) / 2
 
     # ---- end to end with host buffers
-    dev_bufs = [{"q": torch.empty_like(r["q"]), "k": torch.empty_like(r["k"]), "v16": torch.empty_like(r["v"], memory_format=torch.contiguous_format)}
-                for r in inputs]
-    host_out = [torch.empty((B2, l, HEADS, HEAD_DIM), dtype=torch.bfloat16).pin_memory() for l in STEPS_L]
-    e2e_steps = max(1, min(args.steps, 2))
+    host_inputs = [{n: torch.empty(t.shape, dtype=t.dtype).pin_memory().copy_(t) for n, t in r.items() if not n.startswith("_")} for r in inputs]
+    dev_bufs = [{n: torch.empty(t.shape, dtype=t.dtype, device=device) for n, t in r.items()} for r in host_inputs]
+    b2 = 2 * images
+    host_out = [torch.empty((b2, l, w["heads"], w["head_dim"]), dtype=torch.bfloat16).pin_memory() for l in w["steps_l"]]
+    e2e_steps = 1 if args.quick else max(1, min(args.steps, 2))
     side = (torch.cuda.Stream(device), torch.cuda.Stream(device))
-    e2e_step(host_inputs, device, dev_bufs, host_out, side)
+    e2e_step(w, host_inputs, device, dev_bufs, host_out, side)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        h2d, d2h = e2e_step(host_inputs, device, dev_bufs, host_out, side)
+        h2d, d2h = e2e_step(w, host_inputs, device, dev_bufs, host_out, side)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    status = _cabi.device_status()
+    if status != 0:
+        raise SystemExit(f"bench.py: a kernel wait expired during the end-to-end leg (code {status})")
+    del host_inputs, dev_bufs, host_out
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        all_ms = [float(x[0]) for x in gathered]
+        all_e2e = [float(x[1]) for x in gathered]
+    else:
+        all_ms, all_e2e = [ms], [e2e_ms]
+    value = aggregate_throughput([images * args.steps] * world, [m * 1e-3 for m in all_ms])
+    e2e_value = aggregate_throughput([images * e2e_steps] * world, [m * 1e-3 for m in all_e2e])
+    ms, e2e_ms = max(all_ms), max(all_e2e)
+
+    sweep = None
+    if not args.quick and not args.no_sweep:
+        sweep = c5_sweep(device, world, rank, dist)
 
     if rank == 0:
         peaks = load_peaks()
-        kind, si = top
-        lq, lk = STEPS_L[si], sum(STEPS_L[:si + 1])
+        b2 = 2 * images
+        lq, lk = w["steps_l"][si], sum(w["steps_l"][:si + 1])
         if kind == "attn":
-            nbytes = algorithmic_bytes_attn(lq, lk)
-            flops = 4 * B2 * HEADS * lq * lk * HEAD_DIM
-            tensor_bound = flops / nbytes > peaks["tflops"] * 1e12 / (peaks["hbm_gbs"] * 1e9)
+            roof = roof_entry(f"attn[scale {si}: l={lq}, cached={lk}]", w["desc"].split(":")[0], top_ms, peaks,
+                              nbytes=attn_bytes(w, b2, lq, lk), flops=attn_flops(w, b2, lq, lk), kernels=top_launches)
+            key = "attn_tc_kernel" if lq > 16 else "attn_stream_kernel"
+            units, unit_name = b2 * w["heads"], "(sample, head) pairs"
         else:
-            nbytes, flops, tensor_bound = algorithmic_bytes_quant(lq, 4 if kind == "quant_k" else 2), 0, False
-        if tensor_bound:
-            ach = flops / (top_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": ach / peaks["tflops"]}
-        else:
-            ach = nbytes / (top_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"]}
-        # DRAM bytes per launch from one ncu capture of this kernel at a quarter of the batch
-        # (profiles/attn_tc_kernel_var_d16_last_scale.md: 39.2 MB read + 0.03 MB written; traffic scales with batch)
-        traffic = 4 * (39217664 + 33792) if (kind, si) == ("attn", len(STEPS_L) - 1) else None
-        roof.update({"traffic": traffic, "kernel": f"{kind}[scale {si}: l={lq}, cached={lk}]", "launch_ms": top_ms,
-                     "share_of_step": share[top] / sum(share.values()), "peak_source": peaks["source"],
-                     "timing": "CUDA events around 20 back-to-back launches of this kernel on the step's own state",
-                     "algorithmic_bytes": nbytes, "algorithmic_flops": flops})
-        value = world * IMAGES * args.steps / (ms * 1e-3)
+            bits, mode, kw = w["k"] if kind == "quant_k" else w["v"]
+            n_el = b2 * lq * w["heads"] * w["head_dim"]
+            groups = lq * w["heads"] * (w["head_dim"] // kw["group_size"] if kw.get("group_size") else 1) if mode == "G_TOKEN_HEAD" else w["heads"] * w["head_dim"]
+            roof = roof_entry(f"{kind}[scale {si}: l={lq}]", w["desc"].split(":")[0], top_ms, peaks,
+                              nbytes=quant_bytes(n_el, 4 if kind == "quant_k" else 2, bits, groups, kw.get("symmetric", True)), kernels=top_launches)
+            key, units, unit_name = "quant", n_el, "elements"
+        trec, tsrc = load_traffic(f"{key}:{args.workload}")
+        roof["traffic"] = None if trec is None else int(trec["dram_bytes_per_unit"] * units)
+        roof["traffic_source"] = tsrc
+        roof["share_of_step"] = share[top] / sum(share.values())
+        roof["timing"] = "CUDA events around back-to-back launches of this call on the step's own state"
         line = {
-            "metric": "kv_hot_path_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world,
+            "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 codes, fp32 accumulate",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": f"int{w['k'][0]} K / int{w['v'][0]} V codes, fp16 tensor-core operands, fp32 accumulate",
             "data": "synthetic", "impl": "ours",
-            "config": {"workload": WORKLOAD, "images_per_gpu": IMAGES, "tokens": L_TOTAL,
-                       "l2": "per-step inputs total 624 MB > 126 MB L2, no explicit flush",
-                       "launch": "eager" if graph is None else "CUDA graph of one step, replayed"},
-            "clocks": clocks, "gpu_launches": int(launches),
-            "e2e": {"value": world * IMAGES * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
-                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
+            "config": config_of(args.workload, world),
+            "launch": "eager" if not res["graph"] else "CUDA graph of one step, replayed",
+            "clocks": res["clocks"], "gpu_launches": res["launches"],
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
             "roofline": roof,
+            "eager_ms_per_step": eager_ms,
+            "device_status": 0,
+            "oracle_spot_check": {"what": f"bf16 attention output of block {res['keep'][0]}, scale {res['keep'][1]} of the timed run vs the CPU oracle",
+                                  "max_abs": spot_err, "rel_l2": spot_rel},
+            "step_shares": {f"{k}[{s}]": round(v / sum(share.values()), 4) for (k, s), v in sorted(share.items(), key=lambda kv: -kv[1])[:8]},
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(sample_blocks=12)
+        del inputs, res
+        torch.cuda.empty_cache()
+        if world == 1 and not args.quick:
+            line["rooflines"] = kernel_rooflines(device, peaks)
+            others = {}
+            for name in WORKLOADS:
+                if name == args.workload:
+                    continue
+                wo = WORKLOADS[name]
+                r = run_workload(wo, device, args, lib, barrier, steps=3, warmup=3, want_probe=False)
+                rec_o = {"value": wo["images"] * 3 / (r["ms"] * 1e-3), "unit": "images/s", "ms_per_step": r["ms"] / 3, "steps": 3,
+                         "gpu_launches": r["launches"], "workload": wo["desc"]}
+                if name == "var_d16":
+                    rec_o["gpu_eager_baseline"] = gpu_eager_baseline(wo, device, r["inputs"])
+                others[name] = rec_o
+                del r
+                torch.cuda.empty_cache()
+            line["other_workloads"] = others
+            if _cabi.device_status() != 0:
+                raise SystemExit("bench.py: a kernel wait expired in the secondary measurements")
+        if sweep is not None:
+            line["c5_sweep"] = {"what": "Q bf16 [64,16,Lq,D] over 10 521 packed tokens (K channels x20), batch sharded over the ranks, ms = slowest rank",
+                                "rows": sweep}
+        if world == 1 and not args.no_cpu_baseline and not args.quick:
+            line["cpu_baseline"] = cpu_baseline(w, min_seconds=10.0)
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
+def config_of(workload, world):
+    """The `config` object of both arms (identical keys and values, so the two lines can be matched)."""
+    w = WORKLOADS[workload]
+    return {"workload": w["desc"], "name": workload, "images_per_gpu": w["images"], "tokens": sum(w["steps_l"]), "blocks": w["depth"],
+            "l2": "a step's inputs and packed caches exceed the 126 MB L2 many times over; no explicit flush"}
+
+
 # --------------------------------------------------------------------------- CPU arm
-def cpu_blocks(host_inputs, blocks):
-    """The reference algorithm (CPU restatement) for `blocks` blocks of the workload."""
+def cpu_sample(w, host_inputs):
+    """The reference algorithm (CPU restatement) for ONE block of the workload on the sample's batch subset."""
     from oracle import varq_oracle as O
+    (kb, km, kkw), (vb, vm, vkw) = w["k"], w["v"]
+    kq, vq = O.OracleVARQ(kb, w["fmt"], km, **kkw), O.OracleVARQ(vb, w["fmt"], vm, **vkw)
     out = None
-    for _ in range(blocks):
-        kq, vq = O.OracleVARQ(8, "BLHc", "G_TOKEN_HEAD"), O.OracleVARQ(8, "BLHc", "G_TOKEN_HEAD")
-        for rec in host_inputs:
-            k = kq.use_var_q(rec["k"])
-            v = vq.use_var_q(rec["qkv16"][:, :, 2])
-            out = O.attention(rec["q"], k, v, "BLHc", 1.0)
+    for rec in host_inputs:
+        k = kq.use_var_q(rec["k"])
+        v = vq.use_var_q(rec["v"])
+        out = O.attention(rec["q"], k, v, w["fmt"], 1.0)
     return out
 
 
-def cpu_baseline(sample_blocks=1, host_inputs=None):
+def cpu_sample_fraction(w):
+    return (w["cpu_b2"] / (2.0 * w["images"])) * (w["cpu_heads"] / w["heads"]) / w["depth"]
+
+
+def cpu_sample_text(w, cores):
+    return (f"one step = 1 of {w['depth']} blocks on {w['cpu_b2']} of the {2 * w['images']} CFG-doubled samples and "
+            f"{w['cpu_heads']} of the {w['heads']} heads (fraction {cpu_sample_fraction(w):.6f} of a full step; statistics then span "
+            f"the batch subset) on {cores} host threads; "
+            "value = images x fraction / time")
+
+
+def cpu_baseline(w, min_seconds=10.0):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    host_inputs = host_inputs or make_inputs(None, seed=0)
-    t0 = time.perf_counter()
-    cpu_blocks(host_inputs, sample_blocks)
-    dt = time.perf_counter() - t0
-    return {"value": IMAGES / (dt * DEPTH / sample_blocks), "unit": "images/s", "cores": cores, "kind": "port",
-            "sample": f"{sample_blocks} of {DEPTH} blocks of the same workload ({dt:.1f} s), scaled by {DEPTH}/{sample_blocks}"}
+    host_inputs = make_inputs(w, torch.device("cpu"), seed=0, b2=w["cpu_b2"], heads=w["cpu_heads"])
+    n, t0 = 0, time.perf_counter()
+    while True:
+        cpu_sample(w, host_inputs)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            break
+    per = dt / n
+    return {"value": w["images"] * cpu_sample_fraction(w) / per, "unit": "images/s", "cores": cores, "kind": "port",
+            "sample": cpu_sample_text(w, cores) + f"; {n} sample steps in {dt:.1f} s"}
 
 
 def run_reference(args):
@@ -383,44 +783,59 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    w = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    host_inputs = make_inputs(None, seed=0)
-    blocks = 1
-    for _ in range(min(args.warmup, 3)):
-        cpu_blocks(host_inputs, blocks)
-    steps = max(1, min(args.steps, 60))          # one block is about a second of all host cores
+    host_inputs = make_inputs(w, torch.device("cpu"), seed=0, b2=w["cpu_b2"], heads=w["cpu_heads"])
+    for _ in range(args.warmup):
+        cpu_sample(w, host_inputs)
     t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_blocks(host_inputs, blocks)
-    dt = (time.perf_counter() - t0) / steps
-    value = IMAGES / (dt * DEPTH / blocks)
-    sample = f"each step = {blocks} of {DEPTH} blocks of the workload on {cores} host threads, scaled by {DEPTH}/{blocks}; {steps} steps timed"
+    for _ in range(args.steps):
+        cpu_sample(w, host_inputs)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = w["images"] * cpu_sample_fraction(w) / dt
     print(json.dumps({
-        "impl": "reference", "metric": "kv_hot_path_images_per_sec", "value": value, "unit": "images/s",
-        "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 3), "ms_per_step": dt * DEPTH / blocks * 1e3,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference algorithm (the reference is Python and cannot travel to the GPU box)"},
-        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": config_of(args.workload, world),
+        "note": "CPU restatement of the reference algorithm (the reference is Python and cannot travel to the GPU box); "
+                "ms_per_step is the measured time of one sample step, not of a full step",
+        "sample_fraction_of_step": cpu_sample_fraction(w),
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": cpu_sample_text(w, cores)},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
+# --------------------------------------------------------------------------- single-kernel cases (what ncu captures)
 def run_case(name):
-    """One kernel on a small, larger-than-L2 case, a few launches: the command ncu captures."""
+    """One kernel on a small, larger-than-L2 case, a few launches: the command the ncu summaries under profiles/ cite."""
     from VAR_Q.attention import attend_cached
     from VAR_Q.quant import VAR_Q
     dev = torch.device("cuda", 0)
     g = torch.Generator(device=dev).manual_seed(0)
-    if name == "attn":        # the step's last scale at a quarter of the batch: 512 CTAs of the tensor-core kernel
-        B, lq, lk = 16, STEPS_L[-1], L_TOTAL
-        kq = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=lk)
-        vq = VAR_Q(8, "BLHc", "G_TOKEN_HEAD", max_tokens=lk)
-        kq.append(torch.nn.functional.normalize(torch.randn((B, lk, HEADS, HEAD_DIM), generator=g, device=dev), dim=-1))
-        vq.append(torch.randn((B, lk, HEADS, HEAD_DIM), generator=g, device=dev).to(torch.bfloat16))
-        q = torch.nn.functional.normalize(torch.randn((B, lq, HEADS, HEAD_DIM), generator=g, device=dev), dim=-1) * Q_GAIN
+    nbytes = None
+    if name.startswith("attn"):
+        # attn: the VAR-d16 last scale at a quarter of the batch (exact-code K); attn_perdim: VAR-d30 K/V settings, Lq 1024 over
+        # 2240 tokens in ten steps, 8 samples; attn_group: Infinity settings, Lq 1024 over 4096 tokens, 4 samples
+        if name == "attn":
+            B, H, D, fmt, steps, lq = 16, 16, 64, "BLHc", (680,), 256
+            ka, va = (8, "G_TOKEN_HEAD", {}), (8, "G_TOKEN_HEAD", {})
+        elif name == "attn_perdim":
+            B, H, D, fmt, steps, lq = 8, 30, 64, "BLHc", WORKLOADS["var_d30"]["steps_l"], 1024
+            ka, va = WORKLOADS["var_d30"]["k"], WORKLOADS["var_d30"]["v"]
+        else:
+            B, H, D, fmt, steps, lq = 4, 16, 128, "BHLc", (1024, 1024, 2048), 1024
+            ka, va = WORKLOADS["infinity_2b"]["k"], WORKLOADS["infinity_2b"]["v"]
+        kq = VAR_Q(ka[0], fmt, ka[1], max_tokens=sum(steps), **ka[2])
+        vq = VAR_Q(va[0], fmt, va[1], max_tokens=sum(steps), **va[2])
+        for l in steps:
+            shape = (B, l, H, D) if fmt == "BLHc" else (B, H, l, D)
+            kq.append(torch.nn.functional.normalize(torch.randn(shape, generator=g, device=dev), dim=-1))
+            vq.append(torch.randn(shape, generator=g, device=dev).to(torch.bfloat16))
+        qshape = (B, lq, H, D) if fmt == "BLHc" else (B, H, lq, D)
+        q = torch.nn.functional.normalize(torch.randn(qshape, generator=g, device=dev), dim=-1) * Q_GAIN
         fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
-        nbytes = None
     else:                     # "quant": 252 MB of fp32 K, per-head INT8, batch-shared groups; "quant2": per-dim groups (two passes)
         x = torch.randn((128, 256, 30, 64), generator=g, device=dev)
         qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD" if name == "quant" else "G_SCALE_HEAD_DIM", max_tokens=256)
@@ -439,12 +854,16 @@ def run_case(name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the isolated dequant-attention sweep")
+    ap.add_argument("--quick", action="store_true", help="headline measurement only (no per-kernel rooflines, sweep, other workloads, CPU leg)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--case", choices=("attn", "quant", "quant2"), help="run one kernel on a small case and exit (profiling aid)")
+    ap.add_argument("--case", choices=("attn", "attn_perdim", "attn_group", "quant", "quant2"),
+                    help="run one kernel on a small case and exit (profiling aid)")
     args = ap.parse_args()
     if args.case:
         return run_case(args.case)

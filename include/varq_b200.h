@@ -78,8 +78,8 @@ const char* varq_last_error(void);
 uint64_t varq_launch_count(void);
 
 /* Every wait inside the kernels is bounded; a wait that expires makes the kernel record a
- * non-zero code and drain instead of hanging.  This call synchronises with the device's prior
- * work on the current device, returns the first such code since the last call (0 = none) and
+ * non-zero code and drain instead of hanging.  This call waits for all prior work of the current
+ * device (cudaDeviceSynchronize), returns the first such code since the last call (0 = none) and
  * clears it.  HOST pointer.  No counterpart in the reference. */
 int varq_device_status(int32_t* status);
 
@@ -139,6 +139,9 @@ int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int
  *    whose kernels can overlap on the GPU (different streams, or threads racing on one
  *    device) corrupt each other's statistics: serialise them, or use varq_quant_pack
  *    with separate workspaces.
+ *  - groupings that keep (token, head) -- per-token-per-head, with or without groups along head_dim -- run in
+ *    the single-pass kernels and never touch the array: for them this entry point is varq_quant_pack, but the
+ *    size check above still applies to their group count.
  * Results are bit-identical to varq_quant_pack. */
 int varq_quant_pack_static(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D,
                            int32_t bits, int32_t store_bits, float eps,
@@ -154,6 +157,16 @@ int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_t L, int32_
                         int32_t store_bits, const varq_qparams_t* p,
                         const varq_tensor_t* out, void* stream);
 
+/* Pin the kernel varq_attn_fwd uses for every later call of the process: automatic choice, the general
+ * CUDA-core kernel, the streaming CUDA-core kernel or the tensor-core kernel.  A pinned kernel that cannot take
+ * a call (shape, layout) yields to the general kernel.  For tests and measurements that compare the kernels on
+ * one input; no counterpart in the reference. */
+#define VARQ_ATTN_PATH_AUTO   0
+#define VARQ_ATTN_PATH_SMALL  1
+#define VARQ_ATTN_PATH_STREAM 2
+#define VARQ_ATTN_PATH_TC     3
+int varq_attn_force_path(int32_t path);
+
 /* Bytes of scratch varq_attn_fwd needs (partial results of the key-split path). */
 size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
                                  int32_t k_store_bits, int32_t v_store_bits);
@@ -161,6 +174,8 @@ size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, int32_t Lk, i
 /* out = softmax(q k^T * softmax_scale) v over the packed cache, no mask, with
  * k = (k_code - zp_k) * scale_k and v likewise, dequantised on the fly.
  * q, out: (B, Lq, H, D) descriptors; k_codes, v_codes: (B, Lk, H, words) descriptors.
+ * The tensor-core kernel holds queries as fp16 (an fp32 query as an fp16 hi + lo pair): elements saturate
+ * at +-65504, and 16-bit queries below 2^-14 in magnitude lose low bits.
  * Replaces dequant_all() followed by the attention consumer
  * (VAR_Q/quant.py:216-224 + VAR/models/basic_var.py:156-162;
  *  Infinity/infinity/models/basic.py:327-351). */

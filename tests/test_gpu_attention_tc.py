@@ -1,7 +1,5 @@
 """The tensor-core (tcgen05/TMEM) attention kernel, forced for every case, against the oracle
 and against the CUDA-core kernel.  Tolerance: max-abs 2e-3, relative L2 1e-3 (fp32 oracle)."""
-import os
-
 import pytest
 import torch
 
@@ -15,17 +13,13 @@ DEV = "cuda"
 
 
 @pytest.fixture(autouse=True)
-def _path_env():
-    old = os.environ.get("VARQ_ATTN_PATH")
+def _auto_path_afterwards():
     yield
-    if old is None:
-        os.environ.pop("VARQ_ATTN_PATH", None)
-    else:
-        os.environ["VARQ_ATTN_PATH"] = old
+    _cabi.force_attn_path(None)
 
 
 def run(path, q, kq, vq, scale, out_dtype=torch.float32):
-    os.environ["VARQ_ATTN_PATH"] = path
+    _cabi.force_attn_path(path)
     n0 = _cabi.lib().varq_launch_count()
     out = attend_cached(q, kq, vq, scale, out_dtype=out_dtype)
     torch.cuda.synchronize()

@@ -21,7 +21,7 @@ SYMBOLS = (
     "varq_version", "varq_last_error", "varq_launch_count", "varq_device_status", "varq_pack_int8", "varq_unpack_int8",
     "varq_quant_workspace_bytes", "varq_quant_pack", "varq_quant_pack_static",
     "varq_quant_static_scratch_bytes", "varq_unpack_dequant",
-    "varq_attn_workspace_bytes", "varq_attn_fwd",
+    "varq_attn_workspace_bytes", "varq_attn_fwd", "varq_attn_force_path",
 )
 
 
@@ -69,6 +69,8 @@ def _declare(lib):
     lib.varq_unpack_dequant.argtypes = [T, i32, i32, i32, i32, i32, Q, T, vp]
     lib.varq_attn_workspace_bytes.restype = sz
     lib.varq_attn_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, i32]
+    lib.varq_attn_force_path.restype = i32
+    lib.varq_attn_force_path.argtypes = [i32]
     lib.varq_attn_fwd.restype = i32
     lib.varq_attn_fwd.argtypes = [T, T, T, Q, Q, i32, i32, i32, i32, i32, i32, i32, f32, T, vp, sz, vp]
     return lib
@@ -115,13 +117,28 @@ _workspaces = {}
 
 
 def workspace(device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer that only grows (kernels on one stream are ordered)."""
-    key = (device.index if device.index is not None else torch.cuda.current_device())
+    """Scratch buffer of the current stream on `device`; it only grows.
+
+    Kernels on one stream are ordered and may share scratch; kernels on two streams may overlap, so
+    every stream gets its own buffer.  A buffer that is outgrown goes back to torch's caching
+    allocator, which reuses a block only in the order of the stream it was allocated on.
+    """
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        with torch.cuda.device(index):
+            buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+ATTN_PATHS = {None: 0, "auto": 0, "small": 1, "stream": 2, "tc": 3}
+
+
+def force_attn_path(name):
+    """Pin the attention kernel for later calls ("small", "stream", "tc"; None = automatic).  Test hook."""
+    check(lib().varq_attn_force_path(ATTN_PATHS[name]))
 
 
 def device_status() -> int:

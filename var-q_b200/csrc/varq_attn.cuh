@@ -15,6 +15,7 @@ struct AttnArgs {
     int k16, v16;               // 16-byte cp.async usable
     float scale_log2;           // softmax_scale * log2(e)
     int splits, tiles_per_split;
+    int n_qtiles;               // query tiles per (sample, head); grids are 1-D: ((b*H + h) * n_qtiles + qtile) * splits + split
     float* ws;                  // partials: [(b,h,qtile,split)][QT*(2+D)]
 };
 

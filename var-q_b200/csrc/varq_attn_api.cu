@@ -1,9 +1,11 @@
 // C entry points of attention over the packed cache: argument checks and kernel selection.
-#include <cstdlib>
-
 #include "varq_attn.cuh"
 
 using namespace varq;
+
+// Kernel choice pinned by varq_attn_force_path (0 = automatic).  A test hook, not a fallback switch: a pinned
+// kernel that cannot take the call still yields to the general CUDA-core kernel.
+static int g_forced_path = 0;
 
 static bool words_aligned16(const varq_tensor_t* t, int words) {
     return (words % 4 == 0) && aligned16(t->ptr) && (t->stride_b % 4 == 0) && (t->stride_l % 4 == 0) &&
@@ -45,21 +47,27 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     a.out = out->ptr; a.o_dtype = out->dtype; a.os_b = out->stride_b; a.os_l = out->stride_l; a.os_h = out->stride_h;
     a.kc = (const int32_t*)k_codes->ptr; a.ks_b = k_codes->stride_b; a.ks_l = k_codes->stride_l; a.ks_h = k_codes->stride_h;
     a.vc = (const int32_t*)v_codes->ptr; a.vs_b = v_codes->stride_b; a.vs_l = v_codes->stride_l; a.vs_h = v_codes->stride_h;
-    a.kp = make_param_view(kp, false);
-    a.vp = make_param_view(vp, false);
+    a.kp = make_param_view(kp);
+    a.vp = make_param_view(vp);
     a.B = B; a.H = H; a.Lq = Lq; a.Lk = Lk; a.D = D;
     a.wk = wk; a.wv = wv; a.kpitch = wk;
     a.k16 = words_aligned16(k_codes, wk);
     a.v16 = words_aligned16(v_codes, wv);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
-    a.splits = 1; a.tiles_per_split = 0; a.ws = reinterpret_cast<float*>(workspace);
-    // small query counts stay on the CUDA-core kernel (memory-bound); the rest goes to the tensor cores
-    const char* force = getenv("VARQ_ATTN_PATH");       // "small" / "stream" / "tc": testing aid, not a fallback switch
-    const bool want_tc = force ? (force[0] == 't') : (Lq > 8);
+    a.splits = 1; a.tiles_per_split = 0; a.n_qtiles = 1; a.ws = reinterpret_cast<float*>(workspace);
+    // up to 16 queries stay on the CUDA-core kernels (memory-bound); the rest goes to the tensor cores
+    const int force = __atomic_load_n(&g_forced_path, __ATOMIC_RELAXED);
+    const bool want_tc = force ? (force == VARQ_ATTN_PATH_TC) : (Lq > 16);
     if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, (cudaStream_t)stream);
-    const bool want_stream = force ? (force[0] == 's' && force[1] == 't') : (Lq <= 8);
+    const bool want_stream = force ? (force == VARQ_ATTN_PATH_STREAM) : (Lq <= 16);
     if (want_stream && attn_stream_eligible(a, kb, vb)) return attn_stream_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int varq_attn_force_path(int32_t path) {
+    if (path < VARQ_ATTN_PATH_AUTO || path > VARQ_ATTN_PATH_TC) return fail(VARQ_ERR_ARG, "varq_attn_force_path: unknown path %d", path);
+    __atomic_store_n(&g_forced_path, (int)path, __ATOMIC_RELAXED);
+    return VARQ_OK;
 }
 
 extern "C" int varq_device_status(int32_t* status) {

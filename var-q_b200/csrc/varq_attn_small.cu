@@ -68,8 +68,10 @@ __global__ void __launch_bounds__(A1_THREADS) attn_small_kernel(AttnArgs a) {
     uint32_t* sV = sK + 2 * A1_TILE * a.kpitch;                      // [2][TILE][wv]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int split = blockIdx.x, qtile = blockIdx.y;
-    const int bh = blockIdx.z, b = bh / a.H, h = bh - b * a.H;
+    const unsigned blk = blockIdx.x;            // split fastest, then query tile, then (sample, head)
+    const int split = (int)(blk % (unsigned)a.splits);
+    const int qtile = (int)((blk / (unsigned)a.splits) % (unsigned)a.n_qtiles);
+    const int bh = (int)(blk / ((unsigned)a.splits * (unsigned)a.n_qtiles)), b = bh / a.H, h = bh - b * a.H;
     const int q0 = qtile * QT;
     const int nq = min(QT, a.Lq - q0);
 
@@ -287,7 +289,7 @@ __global__ void __launch_bounds__(A1_THREADS) attn_small_kernel(AttnArgs a) {
         if (a.splits == 1) {
             store_o_elem(a.out, a.o_dtype, b * a.os_b + (long long)(q0 + qi) * a.os_l + h * a.os_h + d, o / l);
         } else {
-            float* rec = a.ws + (((long long)bh * gridDim.y + qtile) * a.splits + split) * (QT * (2 + D));
+            float* rec = a.ws + (((long long)bh * a.n_qtiles + qtile) * a.splits + split) * (QT * (2 + D));
             rec[QT * 2 + qi * D + d] = o;
             if (d == 0) { rec[qi] = m; rec[QT + qi] = l; }
         }
@@ -356,7 +358,7 @@ static size_t attn_small_smem(const AttnArgs& a) {
 }
 
 template <int KB, int VB>
-static int launch_small(const AttnArgs& a, cudaStream_t st) {
+static int launch_small(AttnArgs& a, cudaStream_t st) {
     const size_t smem = attn_small_smem(a);
     if (smem > 200 * 1024) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: head_dim %d needs %zu bytes of shared memory", a.D, smem);
     static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
@@ -367,10 +369,10 @@ static int launch_small(const AttnArgs& a, cudaStream_t st) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int nqt = (a.Lq + A1_QT - 1) / A1_QT;
-    if (nqt > 65535 || (long long)a.B * a.H > 65535)
-        return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: grid too large for the small-query path");
-    dim3 grid(a.splits, nqt, a.B * a.H);
-    attn_small_kernel<KB, VB><<<grid, A1_THREADS, smem, st>>>(a);
+    const long long blocks_1d = (long long)a.B * a.H * nqt * a.splits;
+    if (blocks_1d > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
+    a.n_qtiles = nqt;
+    attn_small_kernel<KB, VB><<<(unsigned)blocks_1d, A1_THREADS, smem, st>>>(a);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     if (a.splits > 1) {

@@ -1,4 +1,4 @@
-// Attention over the packed cache for one to four queries: a pure streaming kernel on CUDA cores.
+// Attention over the packed cache for a handful of queries (four per CTA): a pure streaming kernel on CUDA cores.
 //
 // The packed K and V rows of a (sample, head) are contiguous, so a warp reads them straight from
 // global memory, fully coalesced, with no shared-memory staging: every lane owns 16 consecutive
@@ -10,8 +10,9 @@
 // (no cross-lane traffic in the loop) and accumulates P V for its 16 head_dim values.  Lanes,
 // warps and CTAs (key ranges) are merged at the end with the usual log-sum-exp rule; partial
 // results of a split go to the caller's workspace in the layout of the small-query kernel.
-// Applies when the K and V scales are constant along head_dim (per-token-per-head, per-token,
-// per-step); other groupings stay on attn_small_kernel.
+// Applies when a lane's 16 head_dim values share one scale / zero-point, for K and for V: per-token-per-head,
+// per-token and per-step groupings, and groups of 16, 32 or 64 along head_dim (every lane then applies its own
+// group's parameters before the lanes of a key are summed).  Per-dim groupings stay on attn_small_kernel.
 #include <cfloat>
 
 #include "varq_attn.cuh"
@@ -81,14 +82,16 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
     __shared__ float s_part[ST_WARPS][QT][D + 2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int split = blockIdx.x, qtile = blockIdx.y;
-    const int bh = blockIdx.z, b = bh / a.H, h = bh - b * a.H;
+    const unsigned blk = blockIdx.x;            // query tile fastest (tiles of one key range run together and share it in L2)
+    const int qtile = (int)(blk % (unsigned)a.n_qtiles);
+    const int split = (int)((blk / (unsigned)a.n_qtiles) % (unsigned)a.splits);
+    const int bh = (int)(blk / ((unsigned)a.splits * (unsigned)a.n_qtiles)), b = bh / a.H, h = bh - b * a.H;
     const int q0 = qtile * ST_QT;
     const int nq = min(QT, a.Lq - q0);
     const int chunk = lane % LPK, kin = lane / LPK;      // head_dim slice and key slot of this lane
     const int d0 = chunk * 16;
 
-    // the lane's slice of the queries, pre-scaled by softmax_scale * log2(e); full-row sums for the zero-point term
+    // the lane's slice of the queries, pre-scaled by softmax_scale * log2(e), and its sum (zero-point term of the lane's group)
     float q[QT][16], qsum[QT];
 #pragma unroll
     for (int qi = 0; qi < QT; ++qi) {
@@ -105,8 +108,6 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
             q[qi][j + 8] = hi8[j] * a.scale_log2;
             part += q[qi][j] + q[qi][j + 8];
         }
-#pragma unroll
-        for (int m = 1; m < LPK; m <<= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
         qsum[qi] = part;
     }
 
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
             if (ok[u]) {
                 kr[u] = StCodes<KB>::load(kbase + (long long)key * a.ks_l);
                 vr[u] = StCodes<VB>::load(vbase + (long long)key * a.vs_l);
-                const long long pk = a.kp.index(b, a.kp.row(key), h, 0), pv = a.vp.index(b, a.vp.row(key), h, 0);
+                const long long pk = a.kp.index(b, a.kp.row(key), h, d0), pv = a.vp.index(b, a.vp.row(key), h, d0);
                 ksc[u] = __ldg(a.kp.scale + pk);
                 vsc[u] = __ldg(a.vp.scale + pv);
                 if (kz_on) kzp[u] = __ldg(a.kp.zp + pk);
@@ -163,7 +164,8 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
                 float d = 0.f;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) d = fmaf(q[qi][j], kf[j], d);
-                s[qi] = d;
+                // this lane's group: scale_k * (q . code - zp_k * sum q) over its 16 values, already in log2 units
+                s[qi] = ksc[u] * (d - kzp[u] * qsum[qi]);
             }
 #pragma unroll
             for (int m = 1; m < LPK; m <<= 1)
@@ -173,9 +175,7 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
             StCodes<VB>::cvt(vr[u], vf);
 #pragma unroll
             for (int qi = 0; qi < QT; ++qi) {
-                // x = scale_k * (q . code - zp_k * sum q), already in log2 units
-                float x = ksc[u] * (s[qi] - kzp[u] * qsum[qi]);
-                x = ok[u] ? x : -FLT_MAX;
+                const float x = ok[u] ? s[qi] : -FLT_MAX;
                 if (x > m_run[qi] + 8.f) {           // lazy rescale: p stays below 2^8
                     const float alpha = exp2f(m_run[qi] - x);
                     m_run[qi] = x;
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
         if (a.splits == 1) {
             store_o_elem(a.out, a.o_dtype, b * a.os_b + (long long)(q0 + qi) * a.os_l + h * a.os_h + d, num / den);
         } else {
-            float* rec = a.ws + (((long long)bh * gridDim.y + qtile) * a.splits + split) * (ST_QT * (2 + D));
+            float* rec = a.ws + (((long long)bh * a.n_qtiles + qtile) * a.splits + split) * (ST_QT * (2 + D));
             rec[ST_QT * 2 + qi * D + d] = num;
             if (d == 0) { rec[qi] = M; rec[ST_QT + qi] = den; }
         }
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
 // ---------------------------------------------------------------- host side
 bool attn_stream_eligible(const AttnArgs& a, int kb, int vb) {
     if (a.D != 64 && a.D != 128) return false;
-    if (a.kp.group != a.D || a.vp.group != a.D) return false;
+    if (a.kp.group % 16 || a.vp.group % 16) return false;           // a lane's 16 values share their parameters
     const int kw = 16 * kb / 32, vw = 16 * vb / 32;                   // words per lane: loads must be naturally aligned
     auto aligned = [](const void* p, long long sb, long long sl, long long sh, int words) {
         return (reinterpret_cast<uintptr_t>(p) % (words * 4) == 0) && sb % words == 0 && sl % words == 0 && sh % words == 0;
@@ -277,8 +277,10 @@ void attn_small_merge_launch(const AttnArgs& a, int n_qtiles, cudaStream_t st);
 template <int KB, int VB, int D>
 static int launch_stream(AttnArgs& a, int keys_per_split, cudaStream_t st) {
     const int nqt = (a.Lq + ST_QT - 1) / ST_QT;
-    if (nqt > 65535 || (long long)a.B * a.H > 65535) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: grid too large for the streaming path");
-    dim3 grid(a.splits, nqt, a.B * a.H);
+    const long long blocks_1d = (long long)a.B * a.H * nqt * a.splits;
+    if (blocks_1d > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
+    a.n_qtiles = nqt;
+    const unsigned grid = (unsigned)blocks_1d;
     const int qmax = a.Lq < ST_QT ? a.Lq : ST_QT;
     if (qmax == 1) attn_stream_kernel<KB, VB, D, 1><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
     else if (qmax == 2) attn_stream_kernel<KB, VB, D, 2><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);

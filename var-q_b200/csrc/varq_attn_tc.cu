@@ -32,24 +32,6 @@ constexpr int TC_VPROD = 96;      // V-producer threads
 constexpr int TC_M = 128;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
 
-#ifdef VARQ_TC_TRACE
-// development aid: cycle stamps of the last CTA of row 0, [role][tile][event], written to the workspace pointer
-#define TC_TRACE(role, j, ev)                                                                      \
-    do {                                                                                           \
-        if (blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && a.ws && (j) < 32)      \
-            reinterpret_cast<long long*>(a.ws)[((role) * 32 + (j)) * 8 + (ev)] = clock64();        \
-    } while (0)
-#define TC_TRACE_CTA(t0)                                                                                   \
-    do {                                                                                                   \
-        if (threadIdx.x == 0 && a.ws) {                                                                    \
-            const long long id = blockIdx.y * (long long)gridDim.x + blockIdx.x;                           \
-            if (id < 60000) reinterpret_cast<long long*>(a.ws)[4096 + id] = clock64() - (t0);              \
-        }                                                                                                  \
-    } while (0)
-#else
-#define TC_TRACE(role, j, ev) do { } while (0)
-#define TC_TRACE_CTA(t0) do { } while (0)
-#endif
 
 __device__ int g_tc_status = 0;   // first failure code of any launch since the last read (0 = none)
 
@@ -535,7 +517,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh - b * a.H;
+    // query tile fastest: the tiles of one (sample, head) run together and share its packed rows in L2
+    const int qt = (int)(blockIdx.x % (unsigned)a.n_qtiles), bh = (int)(blockIdx.x / (unsigned)a.n_qtiles), b = bh / a.H, h = bh - b * a.H;
     const int q0 = qt * TC_M;
     const int nq = min(TC_M, a.Lq - q0);
     const int T = (a.Lk + N - 1) / N;
@@ -543,9 +526,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 
     const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
     const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
-    if (warp == 0) TC_TRACE(3, 30, 0);
-    const long long cta_t0 = clock64();
-    (void)cta_t0;
     const int aq = (nq + 31) >> 5;                  // TMEM lane quarters that hold real queries
     float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
 
@@ -582,7 +562,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (warp == 0) TC_TRACE(3, 30, 1);
 
     if (warp < 8 || warp == 15) {
         // ---- Q tile -> shared (fp16 hi [, lo]) by the softmax and MMA warps; the producers are already at work
@@ -595,6 +574,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = 0.f;
             if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v);
+            // the operand is fp16: a query element beyond its range (an fp32 or bf16 value above 65504) saturates instead
+            // of becoming infinite
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = fminf(fmaxf(v[j], -65504.f), 65504.f);
             uint32_t hi[4], lo[4];
             float part = 0.f;
 #pragma unroll
@@ -613,7 +596,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         fence_async_smem();
         asm volatile("bar.sync 7, 288;" ::: "memory");
-        if (warp == 0) TC_TRACE(3, 30, 2);
     }
 
     if (warp < 8 && (warp & 3) >= aq) {
@@ -640,20 +622,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         bool ok = true;
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
-            if (quarter == 0) TC_TRACE(half, j, 5);
             // per-key tables visible, S complete, and the P buffer free (the MMA that read it two tiles ago is done)
             ok = ok && mbar_wait3(&bar_t[j & 3], (j >> 2) & 1, &bar_s[buf], (j >> 1) & 1,
                                   &bar_pv[(j - P::PST) & 1], ((j - P::PST) >> 1) & 1, j >= P::PST, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (quarter == 0) TC_TRACE(half, j, 0);
             const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & 3) * 3 * N + half * NH;
             const float* b2 = ks + N;
             const float* kzs = ks + 2 * N;
             const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
             // 32-key chunks of this half that hold at least one key
             const int nch = min(NH / 32, max(0, (min(N, a.Lk - j * N) - half * NH + 31) >> 5));
-            if (quarter == 0) TC_TRACE(half, j, 1);
             if (nch > 0) {
                 tc_fence_after();
                 unsigned char* prow = smem + P::OFF_P + (buf & (P::PST - 1)) * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
@@ -663,7 +642,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     uint32_t rw[32];
                     tmem_ld32(s_addr + c * 32, rw);
                     tmem_wait_ld();
-                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 6);
                     const float cm = k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
                                           : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum);
                     if (m_used == -FLT_MAX) m_used = cm;    // first chunk this thread ever sees: its maximum is the reference
@@ -678,17 +656,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                         c = 0;
                         continue;
                     }
-                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 7);
                     uint32_t ph[16];
                     chunk_exp(rw, m_used, ph);
-                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 2);
                     const int col = half * NH + c * 32;     // key index of the chunk inside the tile
                     unsigned char* blk = prow + (col >> 6) * (TC_M * 128);
                     const int ch0 = (col & 63) >> 3;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
                         sts128(blk + (((ch0 + q4) ^ (r & 7)) << 4), ph[4 * q4], ph[4 * q4 + 1], ph[4 * q4 + 2], ph[4 * q4 + 3]);
-                    if (quarter == 0 && c == 0) TC_TRACE(half, j, 3);
                     ++c;
                 }
                 if (!ok) break;
@@ -696,12 +671,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             fence_async_smem();
             tc_fence_before();
             mbar_arrive(&bar_p[buf]);
-            if (quarter == 0) TC_TRACE(half, j, 4);
         }
         // ---- merge the two halves of a row: o = sum_h w_h (O_h - corr_h) / sum_h w_h L_h, w_h = 2^(m_h - m)
         xch[half * 128 + r] = m_used;
         ok = ok && mbar_wait(bar_o, 0, abort_flag, 14);
-        if (warp == 0) TC_TRACE(3, 30, 3);
         ok = __all_sync(0xffffffffu, ok);
         ok = pair_sync_and(ok);
         if (ok) {
@@ -777,14 +750,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
             const int n_valid = min(N, a.Lk - j * N);
-            if (warp == 8) TC_TRACE(2, j, 0);
             const float sc = nsc, zs = nzs, vsc = nvsc;
             const float bias = (ptid < n_valid) ? 0.f : -1e30f;
             fetch_params(j + 1);
             ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
-            if (warp == 8) TC_TRACE(2, j, 1);
             if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
-            if (warp == 8) TC_TRACE(2, j, 2);
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
             unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
             if (ok) {
@@ -799,7 +769,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, 128, krows);
                     else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, 128, krows);
                 }
-                if (warp == 8) TC_TRACE(2, j, 3);
                 if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
                     float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 3 * N;
                     const float scl = sc * a.scale_log2;
@@ -812,7 +781,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 mbar_arrive(&bar_k[s]);
                 mbar_arrive(&bar_t[j & 3]);
             }
-            if (warp == 8) TC_TRACE(2, j, 4);
             {   // every K producer is done with the packed stage; all 128 take the same decision on `ok`
                 uint32_t all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -871,9 +839,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             for (int i = 0; i < KPT; ++i) { vs[i] = nvs[i]; vz[i] = nvz[i]; }
             fetch_v(j + 1);
             ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
-            if (warp == 12) TC_TRACE(2, j, 5);
             if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
-            if (warp == 12) TC_TRACE(2, j, 6);
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
             unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
@@ -906,7 +872,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 fence_async_smem();
                 mbar_arrive(&bar_v[s]);
             }
-            if (warp == 12) TC_TRACE(2, j, 7);
             {
                 uint32_t all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -941,7 +906,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         auto issue_qk = [&](int j) -> bool {
             const int s = j & 1;
             if (!mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31)) return false;
-            TC_TRACE(3, j, 1);
             tc_fence_after();
             const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
             bool first = true;
@@ -960,7 +924,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 }
             }
             tc_commit(&bar_s[s]);
-            TC_TRACE(3, j, 2);
             return true;
         };
         // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
@@ -991,10 +954,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         for (int jj = 0; jj < T + 2 && ok; ++jj) {
             const int j = jj - 2;
             if (j >= 0) {
-                TC_TRACE(3, jj, 0);
                 ok = mbar_wait(&bar_p[j & 1], (j >> 1) & 1, abort_flag, 32);
                 if (!ok) break;
-                TC_TRACE(3, j, 3);
                 tc_fence_after();
             }
             if (jj < T) {
@@ -1011,10 +972,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         if (ok) tc_commit(bar_o);
         tc_fence_before();
     }
-    if (warp == 0) TC_TRACE(3, 30, 4);
     __syncthreads();
-    if (warp == 0) TC_TRACE(3, 30, 5);
-    TC_TRACE_CTA(cta_t0);
     if (warp == 15) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
@@ -1032,7 +990,8 @@ bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
 }
 
 template <int D, int NQ, bool KS>
-static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
+static int launch_tc(const AttnArgs& a0, int kb, int vb, cudaStream_t st) {
+    AttnArgs a = a0;
     using P = TcPlan<D, NQ, KS>;
     static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
     const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
@@ -1044,16 +1003,19 @@ static int launch_tc(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int nqt = (a.Lq + TC_M - 1) / TC_M;
-    if ((long long)a.B * a.H > 65535) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: batch x heads > 65535");
-    dim3 grid(nqt, a.B * a.H);
-    attn_tc_kernel<D, NQ, KS><<<grid, TC_THREADS, smem, st>>>(a, kb, vb);
+    const long long blocks_1d = (long long)a.B * a.H * nqt;
+    if (blocks_1d > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
+    a.n_qtiles = nqt;
+    attn_tc_kernel<D, NQ, KS><<<(unsigned)blocks_1d, TC_THREADS, smem, st>>>(a, kb, vb);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     return VARQ_OK;
 }
 
 int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
-    const bool split_q = a.q_dtype == VARQ_F32;    // fp16/bf16 queries are exact in one fp16 term
+    // fp16 queries, and bf16 queries inside fp16's normal range (2^-14 <= |q| <= 65504), are exact in one fp16 term;
+    // larger magnitudes saturate, smaller ones lose low bits (both far outside what a softmax can resolve)
+    const bool split_q = a.q_dtype == VARQ_F32;
     const bool split_k = a.kp.group != a.D;        // K scale varies along head_dim: dequantise K, hi + lo tiles
     if (a.D == 64) {
         if (split_k) return split_q ? launch_tc<64, 2, true>(a, kb, vb, st) : launch_tc<64, 1, true>(a, kb, vb, st);
@@ -1065,6 +1027,8 @@ int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
 
 int attn_tc_status(int* out) {
     int v = 0;
+    // a symbol copy on the legacy default stream does not wait for kernels on non-blocking streams: wait for the device first
+    VARQ_CUDA_TRY(cudaDeviceSynchronize());
     VARQ_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)));
     if (v != 0) {
         const int zero = 0;

@@ -122,6 +122,6 @@ struct ParamView {
         return row_of_token ? __ldg(row_of_token + token) : token;
     }
 };
-ParamView make_param_view(const varq_qparams_t* p, bool share_l_is_row0);
+ParamView make_param_view(const varq_qparams_t* p);
 
 }  // namespace varq

@@ -36,13 +36,15 @@ int sm_count() {
     return cached[dev];
 }
 
-ParamView make_param_view(const varq_qparams_t* p, bool share_l_is_row0) {
+// A dim the descriptor marks as shared contributes no stride.  For tokens that holds when no row table is given
+// (one parameter row describes every token); with a row table the rows are per appended step and keep their stride.
+ParamView make_param_view(const varq_qparams_t* p) {
     ParamView v;
     v.scale = p->scale;
     v.zp = p->zp;
     v.row_of_token = p->row_of_token;
     v.sb = p->share_b ? 0 : p->stride_b;
-    v.sr = (share_l_is_row0 && p->share_l) ? 0 : p->stride_r;
+    v.sr = (p->share_l && p->row_of_token == nullptr) ? 0 : p->stride_r;
     v.sh = p->share_h ? 0 : p->stride_h;
     v.sg = p->stride_g;
     v.group = p->group;
@@ -313,7 +315,7 @@ extern "C" int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_
     a.out = out->ptr;
     a.os_b = out->stride_b; a.os_l = out->stride_l; a.os_h = out->stride_h;
     a.B = B; a.L = L; a.H = H; a.D = D; a.words = (D + vpw - 1) / vpw;
-    a.p = make_param_view(p, false);
+    a.p = make_param_view(p);
     const int es = dtype_size(out->dtype);
     const int chunk = (vpw * es) < 16 ? (vpw * es) : 16;
     const bool vec = (D % vpw == 0) && ((reinterpret_cast<uintptr_t>(out->ptr) % chunk) == 0) &&

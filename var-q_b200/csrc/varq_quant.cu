@@ -870,6 +870,7 @@ extern "C" int varq_quant_pack_static(const varq_tensor_t* x, int32_t B, int32_t
                     need / (2 * sizeof(uint32_t)), VARQ_STATIC_SCRATCH_GROUPS);
     uint32_t* scratch = nullptr;
     if (int rc = static_scratch(&scratch)) return rc;
-    // the statistics kernels clear the part of the table they use before accumulating into it
+    // the tables path clears the part of the table it uses on `stream` (a memset node) before accumulating into it;
+    // groupings that run in the single-pass kernels never touch the scratch
     return varq_quant_pack(x, B, L, H, D, bits, store_bits, eps, codes, p, scratch, have, stream);
 }
