@@ -542,7 +542,7 @@ def run_workload(w, device, args, lib, barrier, steps, warmup, want_probe=True, 
 
 def oracle_spot_check(w, res, rank):
     """Attention output of scale 3 of the last block, from the timed run, against the CPU oracle (all blocks see the
-    same inputs, so block 0 of the oracle stands for the last one).  Returns (max-abs error, relative L2)."""
+    same inputs, so block 0 of the oracle stands for the last one).  Returns (max-abs error, relative L2, max |reference|)."""
     from oracle import varq_oracle as O
     (kb, km, kkw), (vb, vm, vkw) = w["k"], w["v"]
     kr, vr = O.OracleVARQ(kb, w["fmt"], km, **kkw), O.OracleVARQ(vb, w["fmt"], vm, **vkw)
@@ -558,7 +558,7 @@ def oracle_spot_check(w, res, rank):
     out = res["kept"].float().cpu()
     err = (out - ref).abs().max().item()
     rel = ((out - ref).norm() / ref.norm().clamp_min(1e-30)).item()
-    return err, rel
+    return err, rel, ref.abs().max().item()
 
 
 def run_ours(args):
@@ -590,8 +590,8 @@ def run_ours(args):
     status = _cabi.device_status()
     if status != 0:
         raise SystemExit(f"bench.py: a kernel wait expired during the timed region (code {status}); the timing is void")
-    spot_err, spot_rel = oracle_spot_check(w, res, rank)
-    if not (spot_err <= 2e-2 and spot_rel <= 1e-2):      # bf16 output: rounding of 2^-9 relative
+    spot_err, spot_rel, spot_max = oracle_spot_check(w, res, rank)
+    if not (spot_err <= 2e-3 + 2.0 ** -8 * spot_max and spot_rel <= 4e-3):      # the output is bf16: up to 2^-8 of its magnitude
         raise SystemExit(f"bench.py: the timed step's output differs from the oracle (max-abs {spot_err:.3e}, rel-L2 {spot_rel:.3e})")
 
     # ---- the dominant launch class alone: back-to-back launches on the state it sees in the step

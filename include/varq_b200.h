@@ -58,13 +58,20 @@ typedef struct {
  * with the stride of a shared dim ignored.  `row` is the token index, or
  * row_of_token[token] when that table is given (modes whose parameters are constant
  * over the tokens of one appended step keep one row per step).
- * zp == NULL means symmetric quantization. */
+ * zp == NULL means symmetric quantization.
+ * row_begin (optional, only read together with row_of_token): row_begin[r] is the first token of row r and
+ * row_begin[n_rows] the number of tokens described, i.e. the inverse of row_of_token for rows that cover
+ * consecutive tokens (one row per appended step).  Attention uses it to cut its key tiles at step boundaries,
+ * which lets per-dim scales that are constant over a step be folded into the queries; without it such
+ * groupings are dequantised element by element. */
 typedef struct {
     float*         scale;
     float*         zp;
     const int32_t* row_of_token;
     int64_t stride_b, stride_r, stride_h, stride_g;
     int32_t share_b, share_l, share_h, group;
+    const int32_t* row_begin;
+    int32_t n_rows, _pad;
 } varq_qparams_t;
 
 /* Version string, static storage. */

@@ -35,7 +35,7 @@ class Guarded:
         return self.payload.data_ptr()
 
     def assert_intact(self, what):
-        sent = torch.full((4,), SENTINEL_I32, dtype=torch.int32).view(torch.uint8)
+        sent = torch.full((1,), SENTINEL_I32, dtype=torch.int32).view(torch.uint8)
         raw = self.raw.view(torch.uint8).cpu()
         es = self.payload.element_size()
         lo, hi = PAD * es, (PAD + self.n) * es

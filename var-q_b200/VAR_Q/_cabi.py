@@ -35,7 +35,8 @@ class QParams(ctypes.Structure):
                 ("stride_b", ctypes.c_int64), ("stride_r", ctypes.c_int64), ("stride_h", ctypes.c_int64),
                 ("stride_g", ctypes.c_int64),
                 ("share_b", ctypes.c_int32), ("share_l", ctypes.c_int32), ("share_h", ctypes.c_int32),
-                ("group", ctypes.c_int32)]
+                ("group", ctypes.c_int32),
+                ("row_begin", ctypes.c_void_p), ("n_rows", ctypes.c_int32), ("_pad", ctypes.c_int32)]
 
 
 _lib = None

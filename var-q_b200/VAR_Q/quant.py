@@ -86,6 +86,7 @@ class VAR_Q:
         self._scale_tbl = self._zp_tbl = None   # fp32 [nB, nH, Rcap, nG]
         self._scale_next = self._zp_next = None
         self._row_of_token = None               # int32 [Lcap] (per-step tables only)
+        self._row_begin = None                  # int32 [Rcap + 1]: first token of every row (per-step tables only)
         self._shape = None                      # (B, H, D)
         self._n_tokens = self._n_rows = 0       # committed by cache()
         self._pending = None                    # (tokens, rows, replaces_cache)
@@ -165,6 +166,11 @@ class VAR_Q:
                 s[:, :, :self._n_rows] = self._scale_tbl[:, :, :self._n_rows]
                 if z is not None:
                     z[:, :, :self._n_rows] = self._zp_tbl[:, :, :self._n_rows]
+            if share_l:
+                rb = torch.zeros((cap + 1,), dtype=torch.int32, device=dev)
+                if self._row_begin is not None and self._n_rows:
+                    rb[:self._n_rows + 1] = self._row_begin[:self._n_rows + 1]
+                self._row_begin = rb
             self._scale_tbl, self._zp_tbl, self._rcap = s, z, cap
             self._scale_next = self._zp_next = None
 
@@ -257,6 +263,7 @@ class VAR_Q:
             self._quantize_into(item, self._codes, self._scale_tbl, self._zp_tbl, self._n_tokens, self._n_rows)
             if share_l:
                 self._row_of_token[self._n_tokens:self._n_tokens + n] = self._n_rows
+                self._row_begin[self._n_rows + 1:self._n_rows + 2].fill_(self._n_tokens + n)   # entry n_rows already holds n_tokens
             self._pending = (n, rows, False)
         self._pack_meta = meta
 
@@ -270,6 +277,7 @@ class VAR_Q:
             self._scale_tbl, self._scale_next = self._scale_next, self._scale_tbl
             self._zp_tbl, self._zp_next = self._zp_next, self._zp_tbl
             self._row_of_token[:n] = 0
+            self._row_begin[1:2].fill_(n)
             self._n_tokens, self._n_rows = n, rows
         else:
             self._n_tokens += n
@@ -321,6 +329,8 @@ class VAR_Q:
         """(codes descriptor, parameter descriptor) of the committed cache, for attention."""
         B, H, D = self._shape
         p = self._param_desc(self._scale_tbl, self._zp_tbl, 0, D, self._row_of_token)
+        if self._row_of_token is not None:
+            p.row_begin, p.n_rows = self._row_begin.data_ptr(), self._n_rows
         return self._codes_desc(self._codes, 0), p
 
     # ------------------------------------------------------------------ reference-shaped views

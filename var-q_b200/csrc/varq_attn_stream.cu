@@ -19,7 +19,8 @@
 
 namespace varq {
 
-constexpr int ST_WARPS = 4;
+constexpr int ST_WARPS = 4;        // warps per CTA for caches that keep four warps busy ...
+constexpr int ST_SHORT_KEYS = 64;  // ... and one-warp CTAs below this many keys (the first scales: a CTA's fixed cost dominates there)
 constexpr int ST_QT = 4;          // query slots (matches the merge kernel's record layout)
 constexpr int ST_UNROLL = 4;      // warp steps in flight
 
@@ -74,12 +75,12 @@ template <> struct StCodes<2> {
     }
 };
 
-template <int KB, int VB, int D, int QT>
-__global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, int keys_per_split) {
+template <int KB, int VB, int D, int QT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) attn_stream_kernel(AttnArgs a, int keys_per_split) {
     constexpr int LPK = D / 16;               // lanes per key
     constexpr int KPS = 32 / LPK;             // keys per warp step
     constexpr int KW = 16 * KB / 32, VW = 16 * VB / 32;   // packed words per lane and step
-    __shared__ float s_part[ST_WARPS][QT][D + 2];
+    __shared__ float s_part[WARPS][QT][D + 2];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const unsigned blk = blockIdx.x;            // query tile fastest (tiles of one key range run together and share it in L2)
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
     // key range of this warp inside the CTA's split
     const int split_begin = split * keys_per_split;
     const int split_end = min(a.Lk, split_begin + keys_per_split);
-    const int per_warp = ((split_end - split_begin + ST_WARPS * KPS - 1) / (ST_WARPS * KPS)) * KPS;
+    const int per_warp = ((split_end - split_begin + WARPS * KPS - 1) / (WARPS * KPS)) * KPS;
     const int w_begin = split_begin + warp * per_warp;
     const int w_end = min(split_end, w_begin + per_warp);
 
@@ -216,15 +217,15 @@ __global__ void __launch_bounds__(ST_WARPS * 32) attn_stream_kernel(AttnArgs a, 
     }
     __syncthreads();
     // ---- merge the warps, then write the output or this split's partial record
-    for (int i = tid; i < QT * D; i += ST_WARPS * 32) {
+    for (int i = tid; i < QT * D; i += WARPS * 32) {
         const int qi = i / D, d = i - qi * D;
         if (qi >= nq) continue;
         float M = -FLT_MAX;
 #pragma unroll
-        for (int w = 0; w < ST_WARPS; ++w) M = fmaxf(M, s_part[w][qi][D]);
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_part[w][qi][D]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int w = 0; w < ST_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float wt = exp2f(s_part[w][qi][D] - M);
             num = fmaf(wt, s_part[w][qi][d], num);
             den = fmaf(wt, s_part[w][qi][D + 1], den);
@@ -251,6 +252,7 @@ bool attn_stream_eligible(const AttnArgs& a, int kb, int vb) {
 }
 
 static int stream_splits(const AttnArgs& a, int& keys_per_split) {
+    if (a.Lk <= ST_SHORT_KEYS) { keys_per_split = ST_SHORT_KEYS; return 1; }     // one warp walks the whole cache
     const int kps = 32 / (a.D / 16);
     const int unit = ST_WARPS * kps * ST_UNROLL;                       // keys one CTA consumes per loop trip
     const long long base = (long long)a.B * a.H * ((a.Lq + ST_QT - 1) / ST_QT);
@@ -282,9 +284,15 @@ static int launch_stream(AttnArgs& a, int keys_per_split, cudaStream_t st) {
     a.n_qtiles = nqt;
     const unsigned grid = (unsigned)blocks_1d;
     const int qmax = a.Lq < ST_QT ? a.Lq : ST_QT;
-    if (qmax == 1) attn_stream_kernel<KB, VB, D, 1><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
-    else if (qmax == 2) attn_stream_kernel<KB, VB, D, 2><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
-    else attn_stream_kernel<KB, VB, D, 4><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
+    if (a.Lk <= ST_SHORT_KEYS) {
+        if (qmax == 1) attn_stream_kernel<KB, VB, D, 1, 1><<<grid, 32, 0, st>>>(a, keys_per_split);
+        else if (qmax == 2) attn_stream_kernel<KB, VB, D, 2, 1><<<grid, 32, 0, st>>>(a, keys_per_split);
+        else attn_stream_kernel<KB, VB, D, 4, 1><<<grid, 32, 0, st>>>(a, keys_per_split);
+    } else {
+        if (qmax == 1) attn_stream_kernel<KB, VB, D, 1, ST_WARPS><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
+        else if (qmax == 2) attn_stream_kernel<KB, VB, D, 2, ST_WARPS><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
+        else attn_stream_kernel<KB, VB, D, 4, ST_WARPS><<<grid, ST_WARPS * 32, 0, st>>>(a, keys_per_split);
+    }
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     if (a.splits > 1) {

@@ -175,7 +175,18 @@ __device__ __forceinline__ uint32_t tile_off(int row, int col, int rows) {
 }
 
 // ---------------------------------------------------------------- shared-memory plan
-template <int D, int NQ, bool KS> struct TcPlan {
+// How K reaches the tensor core:
+//   KM_EXACT  integer codes; one scale / zero-point per key, applied to S in fp32
+//   KM_SPLIT  (code - zp) * scale as an fp16 hi + lo pair of operand tiles, for scales that vary along head_dim per key
+//   KM_FOLD   integer codes; scales that vary along head_dim but are constant over the tokens of an appended step are
+//             folded into the queries (Q * s as fp16 hi + lo, rewritten when a key tile starts a new step), the
+//             zero-point term sum_d q_d s_d z_d is a per-row constant taken off S; key tiles end at step boundaries
+constexpr int KM_EXACT = 0, KM_SPLIT = 1, KM_FOLD = 2;
+constexpr int TC_MAX_TILES = 384;     // entries of the tile schedule (KM_FOLD)
+constexpr int TC_PAR_ENTRIES = 288;   // (key, group) parameter records a producer stages per tile
+
+template <int D, int NQ, int KM> struct TcPlan {
+    static constexpr bool KS = KM == KM_SPLIT;
     static constexpr int N = (D == 64) ? 128 : 64;           // keys per tile
     static constexpr int Q_BYTES = TC_M * D * 2;              // one fp16 Q tile
     static constexpr int KV_BYTES = N * D * 2;                // one fp16 K (or V) tile
@@ -194,9 +205,16 @@ template <int D, int NQ, bool KS> struct TcPlan {
     static constexpr int OFF_BAR = OFF_KS + 4 * 3 * N * 4;    // mbarriers
     static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
-    static constexpr int OFF_XCH = OFF_MISC + 16;             // float [2][128]: the two halves of a row exchange their reference maxima
+    static constexpr int OFF_PREF = OFF_MISC + 16;            // ParamRef [2]: K and V parameter records of the fp32 converters
+    static constexpr int OFF_XCH = OFF_PREF + 2 * 48;         // float [2][128]: the two halves of a row exchange their reference maxima
     static constexpr int OFF_QSUM = OFF_XCH + 2 * 128 * 4;    // float [128]: row sums of Q (zero-point term of K)
-    static constexpr int TOTAL = OFF_QSUM + 128 * 4;
+    static constexpr int OFF_KPAR = OFF_QSUM + 128 * 4;       // uint2 [TC_PAR_ENTRIES]: staged K parameters of the tile being converted
+    static constexpr int OFF_VPAR = OFF_KPAR + TC_PAR_ENTRIES * 8;   // same for V (or fp16 [3][D] when V is per-dim)
+    static constexpr int OFF_KRAW = OFF_VPAR + TC_PAR_ENTRIES * 8;   // float [2][TC_PAR_ENTRIES]: raw scales / zero-points of the next K tile
+    static constexpr int OFF_VRAW = OFF_KRAW + TC_PAR_ENTRIES * 8;   // same for V
+    static constexpr int OFF_ROWC = OFF_VRAW + TC_PAR_ENTRIES * 8;   // KM_FOLD: float [4][128] zero-point constants of the rows, per table slot; float [128] accumulation
+    static constexpr int OFF_TILES = OFF_ROWC + (KM == KM_FOLD ? 5 * 128 * 4 : 0);   // KM_FOLD: int2 [TC_MAX_TILES] (first key, keys << 16 | row)
+    static constexpr int TOTAL = OFF_TILES + (KM == KM_FOLD ? TC_MAX_TILES * 8 : 0);
     // TMEM columns: S double-buffered, then one accumulator per half of the keys:
     // D output columns followed by 16 columns of sum_k P * (small tile)
     static constexpr int ACC_COLS = D + 32;
@@ -213,38 +231,57 @@ __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
     __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
 }
-// four unsigned bytes (each = code + bias) -> 4 halves holding the signed codes
-__device__ __forceinline__ void bytes_to_h4(uint32_t u, uint32_t bias_h2, uint32_t& h01, uint32_t& h23) {
-    h01 = h2_sub(__byte_perm(u, 0x64646464u, 0x4140), bias_h2);
-    h23 = h2_sub(__byte_perm(u, 0x64646464u, 0x4342), bias_h2);
+// four unsigned bytes (each = code + bias) -> 4 halves holding 1024 + code + bias
+__device__ __forceinline__ void bytes_to_raw4(uint32_t u, uint32_t& h01, uint32_t& h23) {
+    h01 = __byte_perm(u, 0x64646464u, 0x4140);
+    h23 = __byte_perm(u, 0x64646464u, 0x4342);
 }
+// Codes<BITS>::raw: one packed word -> 32 / BITS halves holding 1024 + BIAS + code (exact fp16 integers), in field order;
+// cvt: the codes themselves.  A caller that wants code - zp subtracts 1024 + BIAS + zp instead of 1024 + BIAS.
 template <int BITS> struct Codes;
 template <> struct Codes<8> {   // one word -> 4 halves
-    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
-        bytes_to_h4(w ^ 0x80808080u, 0x64806480u, h[0], h[1]);           // 1024 + 128 + c
-    }
+    static constexpr float BIAS = 128.f;
+    static constexpr uint32_t BIAS_H2 = 0x64806480u;                     // 1024 + 128, twice
+    static __device__ __forceinline__ void raw(uint32_t w, uint32_t* h) { bytes_to_raw4(w ^ 0x80808080u, h[0], h[1]); }
 };
 template <> struct Codes<4> {   // one word -> 8 halves
-    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
+    static constexpr float BIAS = 8.f;
+    static constexpr uint32_t BIAS_H2 = 0x64086408u;
+    static __device__ __forceinline__ void raw(uint32_t w, uint32_t* h) {
         const uint32_t x = w ^ 0x88888888u;                               // c + 8 per nibble
         const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu; // fields 0,2,4,6 / 1,3,5,7
-        bytes_to_h4(__byte_perm(lo, hi, 0x5140), 0x64086408u, h[0], h[1]);
-        bytes_to_h4(__byte_perm(lo, hi, 0x7362), 0x64086408u, h[2], h[3]);
+        bytes_to_raw4(__byte_perm(lo, hi, 0x5140), h[0], h[1]);
+        bytes_to_raw4(__byte_perm(lo, hi, 0x7362), h[2], h[3]);
     }
 };
 template <> struct Codes<2> {   // one word -> 16 halves
-    static __device__ __forceinline__ void cvt(uint32_t w, uint32_t* h) {
+    static constexpr float BIAS = 2.f;
+    static constexpr uint32_t BIAS_H2 = 0x64026402u;
+    static __device__ __forceinline__ void raw(uint32_t w, uint32_t* h) {
         const uint32_t x = w ^ 0xAAAAAAAAu;                               // c + 2 per field
         const uint32_t t0 = x & 0x03030303u, t1 = (x >> 2) & 0x03030303u; // fields 0,4,8,12 / 1,5,9,13
         const uint32_t t2 = (x >> 4) & 0x03030303u, t3 = (x >> 6) & 0x03030303u;
         const uint32_t a = __byte_perm(t0, t1, 0x5140), b = __byte_perm(t2, t3, 0x5140);   // f0 f1 f4 f5 / f2 f3 f6 f7
         const uint32_t c = __byte_perm(t0, t1, 0x7362), d = __byte_perm(t2, t3, 0x7362);   // f8 f9 f12 f13 / f10 f11 f14 f15
-        bytes_to_h4(__byte_perm(a, b, 0x5410), 0x64026402u, h[0], h[1]);
-        bytes_to_h4(__byte_perm(a, b, 0x7632), 0x64026402u, h[2], h[3]);
-        bytes_to_h4(__byte_perm(c, d, 0x5410), 0x64026402u, h[4], h[5]);
-        bytes_to_h4(__byte_perm(c, d, 0x7632), 0x64026402u, h[6], h[7]);
+        bytes_to_raw4(__byte_perm(a, b, 0x5410), h[0], h[1]);
+        bytes_to_raw4(__byte_perm(a, b, 0x7632), h[2], h[3]);
+        bytes_to_raw4(__byte_perm(c, d, 0x5410), h[4], h[5]);
+        bytes_to_raw4(__byte_perm(c, d, 0x7632), h[6], h[7]);
     }
 };
+template <int BITS> __device__ __forceinline__ void codes_cvt(uint32_t w, uint32_t* h) {
+    Codes<BITS>::raw(w, h);
+#pragma unroll
+    for (int i = 0; i < 16 / BITS; ++i) h[i] = h2_sub(h[i], Codes<BITS>::BIAS_H2);
+}
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b), *reinterpret_cast<__half2*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
 
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS>
@@ -264,10 +301,10 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
         uint32_t h[4 * HW];
         if (key < n_valid) {
             pk = lds128(packed + key * W + wi);
-            Codes<BITS>::cvt(pk.x, h);
-            Codes<BITS>::cvt(pk.y, h + HW);
-            Codes<BITS>::cvt(pk.z, h + 2 * HW);
-            Codes<BITS>::cvt(pk.w, h + 3 * HW);
+            codes_cvt<BITS>(pk.x, h);
+            codes_cvt<BITS>(pk.y, h + HW);
+            codes_cvt<BITS>(pk.z, h + 2 * HW);
+            codes_cvt<BITS>(pk.w, h + 3 * HW);
         } else {
 #pragma unroll
             for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
@@ -284,20 +321,40 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
 // Scale and zero-point of the VPW values of one packed word, kept in registers while consecutive keys of
 // a thread share their parameter row (groupings with one row per appended step): a thread always converts
 // the same word column of every key it visits, so the parameters change only when the row does.
+// What the fp32 converters need of a ParamView, with the (sample, head) part of the index folded into the pointers: small
+// enough to travel in registers to an out-of-line routine.
+struct ParamRef {     // 40 bytes
+    const float* scale;
+    const float* zp;
+    const int32_t* row_of_token;
+    long long sr, sg;
+    int group;
+    __device__ __forceinline__ int row(int token) const { return row_of_token ? __ldg(row_of_token + token) : token; }
+    __device__ __forceinline__ long long index(int r, int d) const { return r * sr + (long long)(d / group) * sg; }
+};
+__device__ __forceinline__ ParamRef param_ref(const ParamView& pv, int b, int h) {
+    const long long base = pv.index(b, 0, h, 0);
+    ParamRef r;
+    r.scale = pv.scale + base;
+    r.zp = pv.zp ? pv.zp + base : nullptr;
+    r.row_of_token = pv.row_of_token;
+    r.sr = pv.sr; r.sg = pv.sg; r.group = pv.group;
+    return r;
+}
 template <int VPW> struct WordParams {
     float s[VPW], z[VPW];
     int row;
-    __device__ __forceinline__ void fetch(const ParamView& pv, int b, int r, int h, int d0, bool uniform) {
+    __device__ __forceinline__ void fetch(const ParamRef& pv, int r, int d0, bool uniform) {
         row = r;
         if (uniform) {
-            const long long pi = pv.index(b, r, h, d0);
+            const long long pi = pv.index(r, d0);
             const float sv = __ldg(pv.scale + pi), zv = pv.zp ? __ldg(pv.zp + pi) : 0.f;
 #pragma unroll
             for (int j = 0; j < VPW; ++j) { s[j] = sv; z[j] = zv; }
         } else {
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
-                const long long pi = pv.index(b, r, h, d0 + j);
+                const long long pi = pv.index(r, d0 + j);
                 s[j] = __ldg(pv.scale + pi);
                 z[j] = pv.zp ? __ldg(pv.zp + pi) : 0.f;
             }
@@ -311,7 +368,8 @@ template <int VPW> struct WordParams {
 // head_dim (per-dim, group-wise); parameters are fetched per word, or per element when a word spans groups.
 template <int BITS>
 __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W,
-                                             int ptid, const ParamView pv, int b, int h, int k0, int nthr = 128) {
+                                             int ptid, const ParamRef* pv_smem, int k0, int nthr = 128) {
+    const ParamRef pv = *pv_smem;     // the record lives in shared memory so that the call carries one pointer, not ten registers
     constexpr int VPW = 32 / BITS;
     const int total = min(N, (n_valid + 31) & ~31) * W;
     const int wshift = __ffs(W) - 1;          // W is a power of two
@@ -325,7 +383,7 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
         if (key < n_valid) {
             const uint32_t word = packed[idx];
             const int row = pv.row(k0 + key);
-            if (row != wp.row || !fixed_w) wp.fetch(pv, b, row, h, w * VPW, uniform);
+            if (row != wp.row || !fixed_w) wp.fetch(pv, row, w * VPW, uniform);
 #pragma unroll
             for (int j = 0; j < VPW; ++j) hv[j] = __float2half_rn(((float)field<BITS>(word, j) - wp.z[j]) * wp.s[j]);
         } else {
@@ -348,7 +406,8 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
 // group-wise) keep an essentially exact QK^T at the price of a second MMA.
 template <int BITS>
 __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
-                                                   int n_valid, int N, int W, int ptid, const ParamView pv, int b, int h, int k0) {
+                                                   int n_valid, int N, int W, int ptid, const ParamRef* pv_smem, int k0) {
+    const ParamRef pv = *pv_smem;
     constexpr int VPW = 32 / BITS;
     const int total = N * W;
     const int wshift = __ffs(W) - 1;
@@ -362,7 +421,7 @@ __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned
         if (key < n_valid) {
             const uint32_t word = packed[idx];
             const int row = pv.row(k0 + key);
-            if (row != wp.row || !fixed_w) wp.fetch(pv, b, row, h, w * VPW, uniform);
+            if (row != wp.row || !fixed_w) wp.fetch(pv, row, w * VPW, uniform);
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
                 const float k = ((float)field<BITS>(word, j) - wp.z[j]) * wp.s[j];
@@ -384,6 +443,173 @@ __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned
                 *reinterpret_cast<uint4*>(tile_lo + tile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hl + 8 * c8);
             }
         }
+    }
+}
+
+// ---- dequantising producers in packed-half arithmetic.
+// The scale and zero-point of every (key, group) of a tile are staged in shared memory as a record
+//   x = fp16 pair (s_hi, s_lo), s_hi + s_lo = scale to 2^-22;   y = fp16 pair (zb, zb), zb = 1024 + BIAS + zero-point,
+// so that a word's biased codes (1024 + BIAS + code, exact) minus zb are code - zp (exact while |zp| <= 512), and
+//   k_hi = RN(d * s_hi),  k_lo = RN(d * s_lo + (d * s_hi - k_hi))      [the inner residual is exact in fp16]
+// reproduce (code - zp) * scale to 2^-22 with three packed instructions per two elements.  V is one operand tile:
+// RN(d * s_hi + RN(d * s_lo)), i.e. the product rounded once to fp16.
+// A tile that holds a record outside those bounds is converted by the fp32 routines above instead.
+// The raw parameters of the next tile travel global -> shared memory by 4-byte asynchronous copies, so that no register
+// holds them across the out-of-line converter call (a register live across that call is saved to local memory first,
+// which would expose the load's latency).  Entry e = key << g_shift | group; a thread only ever touches its own entries.
+template <int MAXE> struct ParStage {
+    static __device__ __forceinline__ void request(const ParamView& pv, long long base, int k0, int n_valid, int g_shift, int ptid, int nthr,
+                                                   float* raw) {
+#pragma unroll
+        for (int i = 0; i < MAXE; ++i) {
+            const int e = ptid + i * nthr, key = e >> g_shift, g = e & ((1 << g_shift) - 1);
+            if (key < n_valid) {
+                const long long pi = base + pv.row(k0 + key) * pv.sr + (long long)g * pv.sg;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + e)), "l"(pv.scale + pi) : "memory");
+                if (pv.zp) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + MAXE * nthr + e)), "l"(pv.zp + pi) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // waits for this thread's copies, writes its records; returns true if one of them needs the fp32 routine
+    static __device__ __forceinline__ bool build(uint2* par, const float* raw, int n_entries, float bias, bool has_zp, int ptid, int nthr) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        bool slow = false;
+#pragma unroll
+        for (int i = 0; i < MAXE; ++i) {
+            const int e = ptid + i * nthr;
+            if (e >= n_entries) continue;
+            const float sv = raw[e], zv = has_zp ? raw[MAXE * nthr + e] : 0.f;
+            const __half s_hi = __float2half_rn(sv);
+            const __half s_lo = __float2half_rn(sv - __half2float(s_hi));
+            const __half zb = __float2half_rn(1024.f + bias + zv);
+            slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);     // code - zp stays below 2^10, the product inside fp16
+            par[e] = make_uint2((uint32_t)__half_as_ushort(s_hi) | ((uint32_t)__half_as_ushort(s_lo) << 16),
+                                (uint32_t)__half_as_ushort(zb) * 0x10001u);
+        }
+        return slow;
+    }
+};
+
+// K: hi + lo operand tiles from the staged records; each thread converts 16 bytes (4 words) of one key at a time.
+template <int BITS>
+__device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed, const uint2* par,
+                                              int n_valid, int N, int W, int ptid, int g_shift, int grp_shift) {
+    constexpr int VPW = 32 / BITS, HW = VPW / 2;
+    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = N * ipr;
+#pragma unroll 1
+    for (int it = ptid; it < items; it += 128) {
+        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+        uint32_t hi[4 * HW], lo[4 * HW];
+        if (key < n_valid) {
+            const uint4 pk = lds128(packed + key * W + wi);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint2 pr = par[(key << g_shift) + (((wi + q) * VPW) >> grp_shift)];
+                const uint32_t sh = __byte_perm(pr.x, pr.x, 0x1010), sl = __byte_perm(pr.x, pr.x, 0x3232);
+                uint32_t d[HW];
+                Codes<BITS>::raw(wd[q], d);
+#pragma unroll
+                for (int c = 0; c < HW; ++c) {
+                    const uint32_t dz = h2_sub(d[c], pr.y);
+                    const uint32_t h = h2_mul(dz, sh);
+                    const uint32_t e = h2_fma(dz, sh, h ^ 0x80008000u);
+                    hi[q * HW + c] = h;
+                    lo[q * HW + c] = h2_fma(dz, sl, e);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) { hi[i] = 0u; lo[i] = 0u; }
+        }
+        const int d0 = wi * VPW;
+        const uint32_t row = (uint32_t)((d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128);
+        const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+        for (int c = 0; c < HW; ++c) {
+            const uint32_t off = row + (((ch0 + c) ^ (key & 7)) << 4);
+            sts128(tile_hi + off, hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+            sts128(tile_lo + off, lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+        }
+    }
+}
+
+// V: one operand tile RN((code - zp) * scale) from the staged records (rows [n_valid, rows) zero-filled).
+template <int BITS>
+__device__ __noinline__ void group_tile(unsigned char* tile, const uint32_t* packed, const uint2* par, int n_valid, int N, int W,
+                                        int ptid, int nthr, int rows, int g_shift, int grp_shift) {
+    constexpr int VPW = 32 / BITS, HW = VPW / 2;
+    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = rows * ipr;
+#pragma unroll 1
+    for (int it = ptid; it < items; it += nthr) {
+        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+        uint32_t h[4 * HW];
+        if (key < n_valid) {
+            const uint4 pk = lds128(packed + key * W + wi);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint2 pr = par[(key << g_shift) + (((wi + q) * VPW) >> grp_shift)];
+                const uint32_t sh = __byte_perm(pr.x, pr.x, 0x1010), sl = __byte_perm(pr.x, pr.x, 0x3232);
+                uint32_t d[HW];
+                Codes<BITS>::raw(wd[q], d);
+#pragma unroll
+                for (int c = 0; c < HW; ++c) {
+                    const uint32_t dz = h2_sub(d[c], pr.y);
+                    h[q * HW + c] = h2_fma(dz, sh, h2_mul(dz, sl));      // one rounding of (code - zp) * (s_hi + s_lo), to first order
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+        }
+        const int d0 = wi * VPW;
+        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
+        const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+        for (int c = 0; c < HW; ++c)
+            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+    }
+}
+
+// V with one scale / zero-point per head_dim element that all keys of the tile share (per-dim parameters of one appended
+// step): s_h[d] + sl_h[d] = scale as an fp16 hi + lo pair, zb_h[d] = fp16 (1024 + BIAS + zero-point), in shared memory.
+template <int BITS>
+__device__ __noinline__ void perdim_tile(unsigned char* tile, const uint32_t* packed, const __half* s_h, const __half* sl_h, const __half* zb_h,
+                                         int n_valid, int N, int W, int ptid, int nthr, int rows) {
+    constexpr int VPW = 32 / BITS, HW = VPW / 2;
+    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = rows * ipr;
+#pragma unroll 1
+    for (int it = ptid; it < items; it += nthr) {
+        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+        const int d0 = wi * VPW;
+        uint32_t h[4 * HW];
+        if (key < n_valid) {
+            const uint4 pk = lds128(packed + key * W + wi);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            const uint32_t* sp = reinterpret_cast<const uint32_t*>(s_h + d0);
+            const uint32_t* slp = reinterpret_cast<const uint32_t*>(sl_h + d0);
+            const uint32_t* zp = reinterpret_cast<const uint32_t*>(zb_h + d0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t d[HW];
+                Codes<BITS>::raw(wd[q], d);
+#pragma unroll
+                for (int c = 0; c < HW; ++c) {
+                    const uint32_t dz = h2_sub(d[c], zp[q * HW + c]);
+                    h[q * HW + c] = h2_fma(dz, sp[q * HW + c], h2_mul(dz, slp[q * HW + c]));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+        }
+        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
+        const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+        for (int c = 0; c < HW; ++c)
+            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
@@ -497,10 +723,12 @@ __device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const floa
     return m_used;
 }
 
-template <int D, int NQ, bool KS>
+template <int D, int NQ, int KM>
 __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int kb, int vb) {
-    using P = TcPlan<D, NQ, KS>;
+    using P = TcPlan<D, NQ, KM>;
     constexpr int N = P::N;
+    constexpr bool KS = KM == KM_SPLIT, QF = KM == KM_FOLD;
+    static_assert(!QF || NQ == 2, "folded queries are fp16 hi + lo pairs");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // swizzle atoms need 1024-byte alignment
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P::OFF_BAR);
@@ -521,8 +749,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int qt = (int)(blockIdx.x % (unsigned)a.n_qtiles), bh = (int)(blockIdx.x / (unsigned)a.n_qtiles), b = bh / a.H, h = bh - b * a.H;
     const int q0 = qt * TC_M;
     const int nq = min(TC_M, a.Lq - q0);
-    const int T = (a.Lk + N - 1) / N;
     const int wk = a.wk, wv = a.wv;
+    // Key tiles: [j * N, j * N + N) cut at Lk, or (KM_FOLD) the schedule in shared memory whose tiles end at step boundaries
+    const int2* tiles = reinterpret_cast<const int2*>(smem + P::OFF_TILES);
+    int* sched = reinterpret_cast<int*>(smem + P::OFF_MISC + 8);        // KM_FOLD: [0] number of tiles, [1] longest tile
+    auto tile_k0 = [&](int j) -> int { if constexpr (QF) return tiles[j].x; else return j * N; };
+    auto tile_n = [&](int j) -> int { if constexpr (QF) return tiles[j].y >> 16; else return min(N, a.Lk - j * N); };
+    auto tile_row = [&](int j) -> int { return tiles[j].y & 0xffff; };
 
     const int32_t* kbase = a.kc + b * a.ks_b + h * a.ks_h;
     const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
@@ -541,15 +774,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         if (lane == 0) *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        int t_first = (a.Lk + N - 1) / N;
+        if constexpr (QF) {
+            // tile schedule: every row (appended step) is cut into tiles of at most N keys; a lane per row, prefix sums for the slots
+            int2* tw = reinterpret_cast<int2*>(smem + P::OFF_TILES);
+            int n_tiles = 0, longest = 0;
+            for (int r0 = 0; r0 < a.kp.n_rows; r0 += 32) {
+                const int r = r0 + lane;
+                int beg = 0, end = 0;
+                if (r < a.kp.n_rows) { beg = min(__ldg(a.kp.row_begin + r), a.Lk); end = min(__ldg(a.kp.row_begin + r + 1), a.Lk); }
+                const int len = max(end - beg, 0), nt = (len + N - 1) / N;
+                int incl = nt;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += up;
+                }
+                const int base = n_tiles + incl - nt;
+                for (int t = 0; t < nt; ++t)
+                    if (base + t < TC_MAX_TILES) tw[base + t] = make_int2(beg + t * N, (min(N, len - t * N) << 16) | r);
+                n_tiles += __shfl_sync(0xffffffffu, incl, 31);
+                longest = max(longest, __reduce_max_sync(0xffffffffu, min(len, N)));
+            }
+            n_tiles = min(n_tiles, TC_MAX_TILES);      // the host only picks this kernel when the schedule fits
+            if (lane == 0) { sched[0] = n_tiles; sched[1] = longest; }
+            t_first = n_tiles;
+        }
         __syncwarp();
         if (lane == 0) {
             // the first two packed tiles are requested right away; their latency overlaps the rest of the set-up
-            for (int j = 0; j < 2 && j < T; ++j) {
-                const uint32_t rows = (uint32_t)min(N, a.Lk - j * N);
+            for (int j = 0; j < 2 && j < t_first; ++j) {
+                const uint32_t rows = (uint32_t)tile_n(j);
+                const long long k0 = tile_k0(j);
                 mbar_expect_tx(&bar_pk[j], rows * wk * 4);
-                bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + (long long)j * N * wk, rows * wk * 4, &bar_pk[j]);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + k0 * wk, rows * wk * 4, &bar_pk[j]);
                 mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
-                bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, rows * wv * 4, &bar_pkv[j]);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + k0 * wv, rows * wv * 4, &bar_pkv[j]);
             }
         }
     }
@@ -562,8 +822,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const int T = QF ? sched[0] : (a.Lk + N - 1) / N;
+    const int longest_tile = QF ? sched[1] : min(N, a.Lk);
 
-    if (warp < 8 || warp == 15) {
+    if (!QF && (warp < 8 || warp == 15)) {
         // ---- Q tile -> shared (fp16 hi [, lo]) by the softmax and MMA warps; the producers are already at work
         constexpr int CH = D / 8;   // 16-byte chunks per row
         const int qtid = warp < 8 ? tid : 256 + lane;
@@ -617,7 +879,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             return all_ok != 0;
         };
         const bool k_zp = !KS && a.kp.zp != nullptr;      // a dequantised K already carries its zero-point
-        const float qsum = k_zp ? s_qsum[r] : 0.f;
+        float qsum = (k_zp && !QF) ? s_qsum[r] : 0.f;       // KM_FOLD: the row's zero-point constant of the tile's step, read per tile
+        const float* rowc = reinterpret_cast<const float*>(smem + P::OFF_ROWC);
         float m_used = -FLT_MAX;                            // reference maximum of this thread's keys (log2 domain)
         bool ok = true;
         for (int j = 0; j < T; ++j) {
@@ -632,7 +895,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             const float* kzs = ks + 2 * N;
             const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
             // 32-key chunks of this half that hold at least one key
-            const int nch = min(NH / 32, max(0, (min(N, a.Lk - j * N) - half * NH + 31) >> 5));
+            const int nch = min(NH / 32, max(0, (tile_n(j) - half * NH + 31) >> 5));
+            if constexpr (QF) { if (k_zp) qsum = rowc[(j & 3) * 128 + r]; }
             if (nch > 0) {
                 tc_fence_after();
                 unsigned char* prow = smem + P::OFF_P + (buf & (P::PST - 1)) * P::P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
@@ -679,7 +943,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         ok = pair_sync_and(ok);
         if (ok) {
             tc_fence_after();
-            const bool two = a.Lk > NH;                     // the second half of the keys ever held a key
+            const bool two = longest_tile > NH;             // the second half of the keys ever held a key
             const float m_a = half == 0 ? m_used : xch[r], m_b = two ? (half == 1 ? m_used : xch[128 + r]) : -FLT_MAX;
             const float m = fmaxf(m_a, m_b);
             const float w_a = ex2(m_a - m), w_b = two ? ex2(m_b - m) : 0.f;
@@ -722,9 +986,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const int ptid = tid - 256;
         auto issue = [&](int j) {
             const int s = j & 1;
-            const uint32_t kbytes = (uint32_t)min(N, a.Lk - j * N) * wk * 4;
+            const uint32_t kbytes = (uint32_t)tile_n(j) * wk * 4;
             mbar_expect_tx(&bar_pk[s], kbytes);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)j * N * wk, kbytes, &bar_pk[s]);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)tile_k0(j) * wk, kbytes, &bar_pk[s]);
         };
         bool ok = true;
         int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
@@ -734,9 +998,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const long long k_par = a.kp.index(b, 0, h, 0), v_par = a.vp.index(b, 0, h, 0);   // (sample, head) part of the parameter index
         auto fetch_params = [&](int j) {
             nsc = 0.f; nzs = 0.f; nvsc = 1.f;
-            const int key = j * N + ptid;
-            if (j < T && ptid < N && key < a.Lk) {
-                if constexpr (KS) {
+            if (j < T && ptid < tile_n(j)) {
+                const int key = tile_k0(j) + ptid;
+                if constexpr (KM != KM_EXACT) {
                     nsc = 1.f;                       // S needs only softmax_scale * log2(e)
                 } else {
                     const long long pi = k_par + a.kp.row(key) * a.kp.sr;
@@ -747,22 +1011,122 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
         };
         fetch_params(0);
+        // KM_SPLIT: (key, group) records of the tile, staged one tile ahead, for the packed-half converter
+        const int k_vpw = 32 / kb;
+        const int k_ng = D / a.kp.group;                                   // groups per key
+        const bool k_fast = KS && (a.kp.group % k_vpw) == 0 && (a.kp.group & (a.kp.group - 1)) == 0 && N * k_ng <= 2 * 128 && N * k_ng <= TC_PAR_ENTRIES;
+        const int k_gshift = __ffs(k_ng) - 1, k_grp_shift = __ffs(a.kp.group) - 1;
+        uint2* kpar = reinterpret_cast<uint2*>(smem + P::OFF_KPAR);
+        const ParamRef* k_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF);
+        if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF) = param_ref(a.kp, b, h);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        using KStage = ParStage<2>;            // two records per thread: groups of 32 or more at either head_dim
+        float* kraw = reinterpret_cast<float*>(smem + P::OFF_KRAW);
+        if (k_fast) KStage::request(a.kp, k_par, tile_k0(0), tile_n(0), k_gshift, ptid, 128, kraw);
+        // KM_FOLD: the row (appended step) whose scales the Q operand currently carries, and this thread's row constant
+        int q_row = -1;
+        float my_rowc = 0.f;
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
-            const int n_valid = min(N, a.Lk - j * N);
+            const int n_valid = tile_n(j);
+            const int k0 = tile_k0(j);
             const float sc = nsc, zs = nzs, vsc = nvsc;
             const float bias = (ptid < n_valid) ? 0.f : -1e30f;
             fetch_params(j + 1);
+            bool slow = !k_fast;
+            if (KS && k_fast) {
+                slow = KStage::build(kpar, kraw, n_valid << k_gshift, kb == 8 ? 128.f : kb == 4 ? 8.f : 2.f, a.kp.zp != nullptr, ptid, 128);
+                if (j + 1 < T) KStage::request(a.kp, k_par, tile_k0(j + 1), tile_n(j + 1), k_gshift, ptid, 128, kraw);   // consumed one tile later
+            }
             ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
             if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
+            if constexpr (KS) {
+                if (k_fast) {   // records visible to all producers; one record out of bounds sends the whole tile to the fp32 routine
+                    uint32_t any_slow;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(any_slow) : "r"((uint32_t)slow) : "memory");
+                    slow = any_slow != 0;
+                }
+            }
+            if constexpr (QF) {
+                const int row = tile_row(j);
+                if (row != q_row) {
+                    // The tile starts a new step: Q * s(step) replaces the Q operand once S of the previous tile, the last
+                    // reader of the old one, is complete.  c = sum_d q_d s_d z_d of every query row goes to the row constants.
+                    // A thread keeps one 16-byte chunk column; its query chunks are requested eight at a time, ahead of the wait.
+                    constexpr int CH = D / 8;                       // 16-byte chunks per row
+                    constexpr int RSTEP = 128 / CH;                 // rows between two chunks of a thread
+                    constexpr int BATCH = 8;
+                    const int c = ptid % CH, r_first = ptid / CH;
+                    float sv[8], szv[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const long long pi = a.kp.index(b, row, h, c * 8 + e);
+                        sv[e] = __ldg(a.kp.scale + pi);
+                        szv[e] = a.kp.zp ? sv[e] * __ldg(a.kp.zp + pi) : 0.f;
+                    }
+                    float* racc = reinterpret_cast<float*>(smem + P::OFF_ROWC) + 4 * 128;
+                    float v[BATCH][8];
+                    auto load_batch = [&](int it0) {
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            const int r = r_first + (it0 + u) * RSTEP;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
+                            if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v[u]);
+                        }
+                    };
+                    load_batch(0);
+                    if (j >= 1) ok = ok && mbar_wait(&bar_s[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 25);
+#pragma unroll 1
+                    for (int it0 = 0; it0 < TC_M / RSTEP; it0 += BATCH) {
+                        if (it0 > 0) load_batch(it0);
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            const int r = r_first + (it0 + u) * RSTEP;
+                            uint32_t hi[4], lo[4];
+                            float part = 0.f;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                part = fmaf(v[u][e], szv[e], part);
+                                v[u][e] = fminf(fmaxf(v[u][e] * sv[e], -65504.f), 65504.f);
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __half2 hh = __floats2half2_rn(v[u][2 * e], v[u][2 * e + 1]);
+                                const float2 hf = __half22float2(hh);
+                                const __half2 ll = __floats2half2_rn(v[u][2 * e] - hf.x, v[u][2 * e + 1] - hf.y);
+                                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                                lo[e] = *reinterpret_cast<const uint32_t*>(&ll);
+                            }
+                            const uint32_t off = tile_off(r, c * 8, TC_M);
+                            sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
+                            sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
+                            // the CH threads of a row are neighbouring lanes: fold their parts, one of them writes the row's constant
+#pragma unroll
+                            for (int m = 1; m < CH; m <<= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+                            if (c == 0) racc[r] = part;
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    my_rowc = racc[ptid] * a.scale_log2;
+                    q_row = row;
+                }
+                reinterpret_cast<float*>(smem + P::OFF_ROWC)[(j & 3) * 128 + ptid] = my_rowc;
+            }
             const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
             unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
             if (ok) {
                 if constexpr (KS) {
-                    const int k0 = j * N;
-                    if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
-                    else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
-                    else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, a.kp, b, h, k0);
+                    if (!slow) {
+                        if (kb == 8) group_split_tile<8>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
+                        else if (kb == 4) group_split_tile<4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
+                        else group_split_tile<2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
+                    } else {
+                        if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
+                        else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
+                        else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
+                    }
                 } else {
                     const int krows = min(N, ((n_valid + N / 2 - 1) / (N / 2)) * (N / 2));   // softmax reads whole halves of a tile
                     if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, 128, krows);
@@ -775,12 +1139,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     const float vsf = fmaxf(vsc, TC_VS_MIN);
                     tab[ptid] = scl;
                     tab[N + ptid] = bias + __log2f(vsf);
-                    tab[2 * N + ptid] = zs * scl;
+                    tab[2 * N + ptid] = QF ? 1.f : zs * scl;      // KM_FOLD: the row constant is subtracted as it is
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_k[s]);
                 mbar_arrive(&bar_t[j & 3]);
             }
+
             {   // every K producer is done with the packed stage; all 128 take the same decision on `ok`
                 uint32_t all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -802,9 +1167,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         const int ptid = tid - 384;
         auto issue = [&](int j) {
             const int s = j & 1;
-            const uint32_t vbytes = (uint32_t)min(N, a.Lk - j * N) * wv * 4;
+            const uint32_t vbytes = (uint32_t)tile_n(j) * wv * 4;
             mbar_expect_tx(&bar_pkv[s], vbytes);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)j * N * wv, vbytes, &bar_pkv[s]);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)tile_k0(j) * wv, vbytes, &bar_pkv[s]);
         };
         bool ok = true;
         int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
@@ -819,27 +1184,72 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
 #pragma unroll
             for (int i = 0; i < KPT; ++i) {
                 nvs[i] = 1.f; nvz[i] = 0.f;
-                const int kt = ptid + i * TC_VPROD, key = j * N + kt;
-                if (v_exact && j < T && kt < N && key < a.Lk) {
-                    const long long vi = v_par + a.vp.row(key) * a.vp.sr;
+                const int kt = ptid + i * TC_VPROD;
+                if (v_exact && j < T && kt < tile_n(j)) {
+                    const long long vi = v_par + a.vp.row(tile_k0(j) + kt) * a.vp.sr;
                     nvs[i] = __ldg(a.vp.scale + vi);
                     if (a.vp.zp) nvz[i] = __ldg(a.vp.zp + vi);
                 }
             }
         };
         fetch_v(0);
+        // A V scale that varies along head_dim: (key, group) records staged one tile ahead for the packed-half converter,
+        // or, with per-element parameters that a step's tokens share (KM_FOLD tiles lie inside one step), a per-dim table
+        const int v_vpw = 32 / vb;
+        const int v_ng = D / a.vp.group;
+        const bool v_grouped = !v_exact && (a.vp.group % v_vpw) == 0 && (a.vp.group & (a.vp.group - 1)) == 0 && N * v_ng <= 3 * TC_VPROD;
+        const bool v_perdim = QF && !v_exact && !v_grouped && a.vp.row_of_token != nullptr && (D % (4 * v_vpw)) == 0;
+        const int v_gshift = __ffs(v_ng) - 1, v_grp_shift = __ffs(a.vp.group) - 1;
+        uint2* vpar = reinterpret_cast<uint2*>(smem + P::OFF_VPAR);
+        __half* vdim_s = reinterpret_cast<__half*>(smem + P::OFF_VPAR);
+        __half* vdim_sl = vdim_s + D;
+        __half* vdim_zb = vdim_s + 2 * D;
+        const float v_bias = vb == 8 ? 128.f : vb == 4 ? 8.f : 2.f;
+        int vdim_row = -1;
+        const ParamRef* v_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF + 48);
+        if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF + 48) = param_ref(a.vp, b, h);
+        using VStage = ParStage<3>;
+        float* vraw = reinterpret_cast<float*>(smem + P::OFF_VRAW);
+        if (v_grouped) VStage::request(a.vp, v_par, tile_k0(0), tile_n(0), v_gshift, ptid, TC_VPROD, vraw);
         for (int i = ptid; i < 2 * P::AUX_BYTES / 16; i += TC_VPROD) sts128(smem + P::OFF_AUX + i * 16, 0u, 0u, 0u, 0u);
         asm volatile("bar.sync 2, 96;" ::: "memory");
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
-            const int k0 = j * N;
-            const int n_valid = min(N, a.Lk - k0);
+            const int k0 = tile_k0(j);
+            const int n_valid = tile_n(j);
             float vs[KPT], vz[KPT];
 #pragma unroll
             for (int i = 0; i < KPT; ++i) { vs[i] = nvs[i]; vz[i] = nvz[i]; }
             fetch_v(j + 1);
+            bool slow = !v_grouped && !v_perdim;
+            if (v_grouped) {
+                slow = VStage::build(vpar, vraw, n_valid << v_gshift, v_bias, a.vp.zp != nullptr, ptid, TC_VPROD);
+                if (j + 1 < T) VStage::request(a.vp, v_par, tile_k0(j + 1), tile_n(j + 1), v_gshift, ptid, TC_VPROD, vraw);   // consumed one tile later
+            } else if (v_perdim) {
+                const int row = a.vp.row(k0);
+                slow = a.vp.row(k0 + n_valid - 1) != row;            // the tile must lie inside one row of V's parameters
+                if (!slow && row != vdim_row) {
+                    for (int d = ptid; d < D; d += TC_VPROD) {
+                        const long long pi = a.vp.index(b, row, h, d);
+                        const float sv = __ldg(a.vp.scale + pi), zv = a.vp.zp ? __ldg(a.vp.zp + pi) : 0.f;
+                        const __half s_hi = __float2half_rn(sv);
+                        vdim_s[d] = s_hi;
+                        vdim_sl[d] = __float2half_rn(sv - __half2float(s_hi));
+                        vdim_zb[d] = __float2half_rn(1024.f + v_bias + zv);
+                        slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);
+                    }
+                }
+                vdim_row = slow ? -1 : row;
+            }
             ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
             if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
+            if (v_grouped || v_perdim) {   // tables visible to all producers; they agree on the converter
+                uint32_t any_slow;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(any_slow) : "r"((uint32_t)slow) : "memory");
+                slow = any_slow != 0;
+                if (slow) vdim_row = -1;
+            }
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
             unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
@@ -848,10 +1258,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                     else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                     else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                } else if (!slow && v_grouped) {
+                    if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
+                    else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
+                    else group_tile<2>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
+                } else if (!slow && v_perdim) {
+                    if (vb == 8) perdim_tile<8>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else if (vb == 4) perdim_tile<4>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else perdim_tile<2>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
                 } else {
-                    if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
-                    else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
-                    else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, a.vp, b, h, k0, TC_VPROD);
+                    if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
+                    else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
+                    else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
                 }
                 unsigned char* aux = smem + P::OFF_AUX + s * P::AUX_BYTES;
 #pragma unroll
@@ -872,6 +1290,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 fence_async_smem();
                 mbar_arrive(&bar_v[s]);
             }
+
             {
                 uint32_t all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -908,49 +1327,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (!mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31)) return false;
             tc_fence_after();
             const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
-            bool first = true;
+            // the k-step loop stays rolled (descriptors advance by increments): unrolled, its 64-bit descriptor constants
+            // spill, and the issuing thread is the one thread everybody waits for
+            uint64_t qk = qd0, kk_d = kd;
+#pragma unroll 1
+            for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-            for (int qi = 0; qi < NQ; ++qi) {
+                for (int qi = 0; qi < NQ; ++qi) {
 #pragma unroll
-                for (int ki = 0; ki < P::KT; ++ki) {
-                    if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
-                    const uint64_t qd = qd0 + (uint64_t)((qi * P::Q_BYTES) >> 4), kdk = kd + (uint64_t)((ki * P::KV_BYTES) >> 4);
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        tc_mma_f16(tmem_base + P::COL_S + s * N, qd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
-                                   kdk + (uint64_t)(((kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S, first ? 0u : 1u);
-                        first = false;
+                    for (int ki = 0; ki < P::KT; ++ki) {
+                        if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
+                        tc_mma_f16(tmem_base + P::COL_S + s * N, qk + (uint64_t)((qi * P::Q_BYTES) >> 4),
+                                   kk_d + (uint64_t)((ki * P::KV_BYTES) >> 4), IDESC_S, (kk == 0 && qi == 0 && ki == 0) ? 0u : 1u);
                     }
                 }
+                // next 16 head_dim values: 32 bytes further inside the 64-column block, a new block every fourth step
+                const bool wrap = (kk & 3) == 3;
+                qk += wrap ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
+                kk_d += wrap ? (uint64_t)((N * 128 - 96) >> 4) : 2u;
             }
             tc_commit(&bar_s[s]);
             return true;
         };
         // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
         // half of a tile's keys goes to accumulator 0, the second half to accumulator 1
+        // MMAs of one shape are issued together: a change of instruction shape between consecutive MMAs costs the tensor
+        // pipe a few hundred cycles, so a tile's O products go first and its normaliser products after them.
+        bool o_live[2] = {false, false}, x_live[2] = {false, false};
         auto issue_pv = [&](int j) {
             const int s = j & 1;
-            const int ksteps = (min(N, a.Lk - j * N) + 15) >> 4;     // P columns / V rows past the keys are never read
+            const int ksteps = (tile_n(j) + 15) >> 4;                // P columns / V rows past the keys are never read
             const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
             const uint64_t ad = ad0 + (uint64_t)((s * P::AUX_BYTES) >> 4);
-            // rolled on purpose: the loop is short-lived code that every CTA has to fetch again
-            uint64_t pk = pd, vk = vd, ak = ad;
+            // rolled on purpose: the loops are short-lived code that every CTA has to fetch again
+            uint64_t pk = pd, vk = vd;
 #pragma unroll 1
             for (int kk = 0; kk < ksteps; ++kk) {
                 const int hf = kk >= N / 32 ? 1 : 0;
-                const uint32_t acc = tmem_base + P::COL_O + hf * P::ACC_COLS;
-                const uint32_t accum = (j > 0 || kk > hf * (N / 32)) ? 1u : 0u;
-                tc_mma_f16(acc, pk, vk, IDESC_O, accum);
-                tc_mma_f16(acc + D, pk, ak, IDESC_AUX, accum);
-                // next 16 keys: 32 bytes further in the K-major tiles (a new 64-key block every fourth step), 16 rows in V
+                // the first product into an accumulator overwrites it (with tiles cut at step boundaries the second
+                // half of the keys may first appear in a later tile than the first half)
+                tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS, pk, vk, IDESC_O, o_live[hf] ? 1u : 0u);
+                o_live[hf] = true;
+                // next 16 keys: 32 bytes further in the K-major tile (a new 64-key block every fourth step), 16 rows in V
+                pk += ((kk & 3) == 3) ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
+                vk += (uint64_t)(2048 >> 4);
+            }
+            uint64_t ak = ad;
+            pk = pd;
+#pragma unroll 1
+            for (int kk = 0; kk < ksteps; ++kk) {
+                const int hf = kk >= N / 32 ? 1 : 0;
+                tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS + D, pk, ak, IDESC_AUX, x_live[hf] ? 1u : 0u);
+                x_live[hf] = true;
                 const bool wrap = (kk & 3) == 3;
                 pk += wrap ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
                 ak += wrap ? (uint64_t)((2048 - 96) >> 4) : 2u;
-                vk += (uint64_t)(2048 >> 4);
             }
             tc_commit(&bar_pv[s]);
         };
-        // iteration jj issues S(jj) for jj < 2 (nothing to wait for) and from then on: wait P(j), S(j + 2), O += P(j) V(j), j = jj - 2
+        // Iteration jj issues S(jj) for jj < 2 (nothing to wait for) and from then on waits for P(j), j = jj - 2, and issues
+        // S(j + 2) and O += P(j) V(j).  With two P buffers S goes first: the softmax two tiles ahead waits for it while nobody
+        // waits for the accumulator.  With one P buffer the next softmax waits for this product to free the buffer, so it goes first.
         for (int jj = 0; jj < T + 2 && ok; ++jj) {
             const int j = jj - 2;
             if (j >= 0) {
@@ -958,11 +1395,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 if (!ok) break;
                 tc_fence_after();
             }
+            if (P::PST == 1 && j >= 0) {
+                ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, 34);
+                if (!ok) break;
+                tc_fence_after();
+                issue_pv(j);
+            }
             if (jj < T) {
                 ok = issue_qk(jj);
                 if (!ok) break;
             }
-            if (j >= 0) {
+            if (P::PST == 2 && j >= 0) {
                 ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, 34);
                 if (!ok) break;
                 tc_fence_after();
@@ -989,24 +1432,24 @@ bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
     return true;
 }
 
-template <int D, int NQ, bool KS>
+template <int D, int NQ, int KM>
 static int launch_tc(const AttnArgs& a0, int kb, int vb, cudaStream_t st) {
     AttnArgs a = a0;
-    using P = TcPlan<D, NQ, KS>;
+    using P = TcPlan<D, NQ, KM>;
     static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
     const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
     static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
     int dev = 0;
     VARQ_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        VARQ_CUDA_TRY(cudaFuncSetAttribute(attn_tc_kernel<D, NQ, KM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int nqt = (a.Lq + TC_M - 1) / TC_M;
     const long long blocks_1d = (long long)a.B * a.H * nqt;
     if (blocks_1d > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
     a.n_qtiles = nqt;
-    attn_tc_kernel<D, NQ, KS><<<(unsigned)blocks_1d, TC_THREADS, smem, st>>>(a, kb, vb);
+    attn_tc_kernel<D, NQ, KM><<<(unsigned)blocks_1d, TC_THREADS, smem, st>>>(a, kb, vb);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     return VARQ_OK;
@@ -1016,13 +1459,19 @@ int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
     // fp16 queries, and bf16 queries inside fp16's normal range (2^-14 <= |q| <= 65504), are exact in one fp16 term;
     // larger magnitudes saturate, smaller ones lose low bits (both far outside what a softmax can resolve)
     const bool split_q = a.q_dtype == VARQ_F32;
-    const bool split_k = a.kp.group != a.D;        // K scale varies along head_dim: dequantise K, hi + lo tiles
+    const bool varies = a.kp.group != a.D;         // K scale varies along head_dim
+    // ... but is constant over the tokens of a step, the steps are known, and their tile schedule fits: fold it into Q
+    const int n_max = a.D == 64 ? 128 : 64;
+    const bool fold = varies && a.kp.row_of_token && a.kp.row_begin && a.kp.n_rows > 0 && a.kp.n_rows <= 0xffff &&
+                      (a.Lk + n_max - 1) / n_max + a.kp.n_rows <= TC_MAX_TILES;
     if (a.D == 64) {
-        if (split_k) return split_q ? launch_tc<64, 2, true>(a, kb, vb, st) : launch_tc<64, 1, true>(a, kb, vb, st);
-        return split_q ? launch_tc<64, 2, false>(a, kb, vb, st) : launch_tc<64, 1, false>(a, kb, vb, st);
+        if (fold) return launch_tc<64, 2, KM_FOLD>(a, kb, vb, st);
+        if (varies) return split_q ? launch_tc<64, 2, KM_SPLIT>(a, kb, vb, st) : launch_tc<64, 1, KM_SPLIT>(a, kb, vb, st);
+        return split_q ? launch_tc<64, 2, KM_EXACT>(a, kb, vb, st) : launch_tc<64, 1, KM_EXACT>(a, kb, vb, st);
     }
-    if (split_k) return split_q ? launch_tc<128, 2, true>(a, kb, vb, st) : launch_tc<128, 1, true>(a, kb, vb, st);
-    return split_q ? launch_tc<128, 2, false>(a, kb, vb, st) : launch_tc<128, 1, false>(a, kb, vb, st);
+    if (fold) return launch_tc<128, 2, KM_FOLD>(a, kb, vb, st);
+    if (varies) return split_q ? launch_tc<128, 2, KM_SPLIT>(a, kb, vb, st) : launch_tc<128, 1, KM_SPLIT>(a, kb, vb, st);
+    return split_q ? launch_tc<128, 2, KM_EXACT>(a, kb, vb, st) : launch_tc<128, 1, KM_EXACT>(a, kb, vb, st);
 }
 
 int attn_tc_status(int* out) {

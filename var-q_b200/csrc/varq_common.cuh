@@ -113,6 +113,8 @@ struct ParamView {
     const float* scale;
     const float* zp;
     const int32_t* row_of_token;
+    const int32_t* row_begin;      // first token of every row (n_rows + 1 entries), or null
+    int n_rows;
     long long sb, sr, sh, sg;
     int group;
     __device__ __forceinline__ long long index(int b, int row, int h, int d) const {

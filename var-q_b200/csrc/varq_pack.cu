@@ -43,6 +43,8 @@ ParamView make_param_view(const varq_qparams_t* p) {
     v.scale = p->scale;
     v.zp = p->zp;
     v.row_of_token = p->row_of_token;
+    v.row_begin = (p->row_of_token && p->n_rows > 0) ? p->row_begin : nullptr;
+    v.n_rows = v.row_begin ? p->n_rows : 0;
     v.sb = p->share_b ? 0 : p->stride_b;
     v.sr = (p->share_l && p->row_of_token == nullptr) ? 0 : p->stride_r;
     v.sh = p->share_h ? 0 : p->stride_h;
