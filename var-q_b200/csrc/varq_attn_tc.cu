@@ -156,9 +156,16 @@ __device__ __forceinline__ float pick(const float4& v, int i) { return i == 0 ? 
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 format:
 // [0,14) start >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4 |
 // [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout = 2u) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+// The V operand (B of O += P V, MN-major: row = key, column = head_dim) is kept UNSWIZZLED (layout type 0): 8 x 8 core
+// matrices of 128 contiguous bytes (8 keys x 16 bytes), key blocks 128 bytes apart, 8-column blocks N * 16 bytes apart.
+// Without the 64-column atoms of the swizzled layouts the tile can be D + 16 columns wide: the last 16 columns carry
+// the per-key normaliser terms, so one MMA per 16 keys produces the output and the normaliser sums together.
+__device__ __forceinline__ uint32_t vtile_off(int key, int d0, int N) {      // byte offset of the 16-byte chunk (key, d0 .. d0 + 7)
+    return (uint32_t)((d0 >> 3) * (N * 16) + (key >> 3) * 128 + (key & 7) * 16);
 }
 // Instruction descriptor, kind::f16: fp16 A and B, fp32 accumulator.
 // [4,6) c format (1 = f32) | [7,10) a format (0 = f16) | [10,13) b format | 15 a major | 16 b major
@@ -189,7 +196,8 @@ template <int D, int NQ, int KM> struct TcPlan {
     static constexpr bool KS = KM == KM_SPLIT;
     static constexpr int N = (D == 64) ? 128 : 64;           // keys per tile
     static constexpr int Q_BYTES = TC_M * D * 2;              // one fp16 Q tile
-    static constexpr int KV_BYTES = N * D * 2;                // one fp16 K (or V) tile
+    static constexpr int KV_BYTES = N * D * 2;                // one fp16 K tile
+    static constexpr int V_BYTES = N * (D + 16) * 2;          // one fp16 V tile with its 16 normaliser columns
     static constexpr int P_BYTES = TC_M * N * 2;
     static constexpr int PK_BYTES = N * D;                    // packed staging at 8 bits (largest)
     static constexpr int KT = KS ? 2 : 1;                     // K operand tiles per stage (hi, lo when K is dequantised)
@@ -197,11 +205,9 @@ template <int D, int NQ, int KM> struct TcPlan {
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = OFF_Q + NQ * Q_BYTES;        // [2][KT]
     static constexpr int OFF_V = OFF_K + 2 * KT * KV_BYTES;   // [2]
-    static constexpr int OFF_P = OFF_V + 2 * KV_BYTES;        // [PST]
+    static constexpr int OFF_P = (OFF_V + 2 * V_BYTES + 1023) / 1024 * 1024;   // [PST]
     static constexpr int OFF_PK = OFF_P + PST * P_BYTES;      // [2][K, V]
-    static constexpr int AUX_BYTES = (N / 64) * 16 * 128;     // 16 x N fp16, K-major: rows 0-3 = 1/V-scale hi, lo, V zero-point hi, lo
-    static constexpr int OFF_AUX = OFF_PK + 4 * PK_BYTES;     // [2], written with the V stage of the same tile
-    static constexpr int OFF_KS = OFF_AUX + 2 * AUX_BYTES;    // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
+    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
     static constexpr int OFF_BAR = OFF_KS + 4 * 3 * N * 4;    // mbarriers
     static constexpr int N_BARS = 19;
     static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
@@ -284,7 +290,7 @@ __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
 }
 
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
-template <int BITS>
+template <int BITS, bool VL = false>      // VL: the unswizzled V layout
 __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
                                            int rows = -1) {
     // rows [n_valid, rows) are zero-filled; consumers never read past `rows`
@@ -310,11 +316,17 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
             for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
         }
         const int d0 = wi * VPW;              // first head_dim index of the item
-        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
-        const int ch0 = (d0 & 63) >> 3;
+        if constexpr (VL) {
+            unsigned char* base = tile + vtile_off(key, d0, N);
 #pragma unroll
-        for (int c = 0; c < HW; ++c)         // HW chunks of 8 halves
-            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+            for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+        } else {
+            unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
+            const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+            for (int c = 0; c < HW; ++c)         // HW chunks of 8 halves
+                sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+        }
     }
 }
 
@@ -392,11 +404,11 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
         }
         const int d0 = w * VPW;
         if constexpr (VPW == 4) {
-            *reinterpret_cast<uint2*>(tile + tile_off(key, d0, N)) = *reinterpret_cast<uint2*>(hv);
+            *reinterpret_cast<uint2*>(tile + vtile_off(key, d0, N) + (d0 & 7) * 2) = *reinterpret_cast<uint2*>(hv);
         } else {
 #pragma unroll
             for (int c8 = 0; c8 < VPW / 8; ++c8)
-                *reinterpret_cast<uint4*>(tile + tile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hv + 8 * c8);
+                *reinterpret_cast<uint4*>(tile + vtile_off(key, d0 + 8 * c8, N)) = *reinterpret_cast<uint4*>(hv + 8 * c8);
         }
     }
 }
@@ -565,11 +577,9 @@ __device__ __noinline__ void group_tile(unsigned char* tile, const uint32_t* pac
             for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
         }
         const int d0 = wi * VPW;
-        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
-        const int ch0 = (d0 & 63) >> 3;
+        unsigned char* base = tile + vtile_off(key, d0, N);
 #pragma unroll
-        for (int c = 0; c < HW; ++c)
-            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+        for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
@@ -605,11 +615,9 @@ __device__ __noinline__ void perdim_tile(unsigned char* tile, const uint32_t* pa
 #pragma unroll
             for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
         }
-        unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
-        const int ch0 = (d0 & 63) >> 3;
+        unsigned char* base = tile + vtile_off(key, d0, N);
 #pragma unroll
-        for (int c = 0; c < HW; ++c)
-            sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+        for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
@@ -1085,20 +1093,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                         for (int u = 0; u < BATCH; ++u) {
                             const int r = r_first + (it0 + u) * RSTEP;
                             uint32_t hi[4], lo[4];
-                            float part = 0.f;
+                            float p0 = 0.f, p1 = 0.f;
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                part = fmaf(v[u][e], szv[e], part);
-                                v[u][e] = fminf(fmaxf(v[u][e] * sv[e], -65504.f), 65504.f);
-                            }
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const __half2 hh = __floats2half2_rn(v[u][2 * e], v[u][2 * e + 1]);
+                            for (int e = 0; e < 4; ++e) {      // packed fp32 pairs: two elements per instruction
+                                float x0, x1;
+                                fma2(p0, p1, v[u][2 * e], v[u][2 * e + 1], szv[2 * e], szv[2 * e + 1], p0, p1);
+                                fma2(x0, x1, v[u][2 * e], v[u][2 * e + 1], sv[2 * e], sv[2 * e + 1], 0.f, 0.f);
+                                x0 = fminf(fmaxf(x0, -65504.f), 65504.f);      // saturate instead of overflowing fp16
+                                x1 = fminf(fmaxf(x1, -65504.f), 65504.f);
+                                const __half2 hh = __floats2half2_rn(x0, x1);
                                 const float2 hf = __half22float2(hh);
-                                const __half2 ll = __floats2half2_rn(v[u][2 * e] - hf.x, v[u][2 * e + 1] - hf.y);
+                                float y0, y1;
+                                add2(y0, y1, x0, x1, -hf.x, -hf.y);
+                                const __half2 ll = __floats2half2_rn(y0, y1);
                                 hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
                                 lo[e] = *reinterpret_cast<const uint32_t*>(&ll);
                             }
+                            float part = p0 + p1;
                             const uint32_t off = tile_off(r, c * 8, TC_M);
                             sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
                             sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
@@ -1211,7 +1222,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         using VStage = ParStage<3>;
         float* vraw = reinterpret_cast<float*>(smem + P::OFF_VRAW);
         if (v_grouped) VStage::request(a.vp, v_par, tile_k0(0), tile_n(0), v_gshift, ptid, TC_VPROD, vraw);
-        for (int i = ptid; i < 2 * P::AUX_BYTES / 16; i += TC_VPROD) sts128(smem + P::OFF_AUX + i * 16, 0u, 0u, 0u, 0u);
         asm volatile("bar.sync 2, 96;" ::: "memory");
         for (int j = 0; j < T; ++j) {
             const int s = j & 1;
@@ -1252,12 +1262,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
             const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
             const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
-            unsigned char* tv = smem + P::OFF_V + s * P::KV_BYTES;
+            unsigned char* tv = smem + P::OFF_V + s * P::V_BYTES;
             if (ok) {
                 if (v_exact) {
-                    if (vb == 8) codes_tile<8>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else if (vb == 4) codes_tile<4>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else codes_tile<2>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    if (vb == 8) codes_tile<8, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else if (vb == 4) codes_tile<4, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    else codes_tile<2, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
                 } else if (!slow && v_grouped) {
                     if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
                     else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
@@ -1271,20 +1281,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
                     else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
                 }
-                unsigned char* aux = smem + P::OFF_AUX + s * P::AUX_BYTES;
+                // normaliser columns D .. D + 15 of every key of the tile: 2^-6 / V scale and 2^-8 * V zero-point as fp16 hi + lo
+                // pairs, twelve zeros (every row gets finite values: P is zero for the keys past the end, but 0 * NaN is not)
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) {
                     const int kt = ptid + i * TC_VPROD;
                     if (kt < N) {
                         const float vin = TC_AUX_DOWN / fmaxf(vs[i], TC_VS_MIN), vzd = vz[i] * TC_ZP_DOWN;
                         const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
-                        // element (row, kt) of the 16-row tile: rows 0-3 differ in the row offset and the swizzled chunk only
-                        unsigned char* col = aux + (kt >> 6) * (16 * 128) + ((kt & 7) << 1);
-                        const int ch = (kt & 63) >> 3;
-                        *reinterpret_cast<__half*>(col + ((ch ^ 0) << 4)) = vin_hi;
-                        *reinterpret_cast<__half*>(col + 128 + ((ch ^ 1) << 4)) = __float2half_rn(vin - __half2float(vin_hi));
-                        *reinterpret_cast<__half*>(col + 256 + ((ch ^ 2) << 4)) = vz_hi;
-                        *reinterpret_cast<__half*>(col + 384 + ((ch ^ 3) << 4)) = __float2half_rn(vzd - __half2float(vz_hi));
+                        const __half vin_lo = __float2half_rn(vin - __half2float(vin_hi)), vz_lo = __float2half_rn(vzd - __half2float(vz_hi));
+                        unsigned char* ax = tv + vtile_off(kt, D, N);
+                        sts128(ax, (uint32_t)__half_as_ushort(vin_hi) | ((uint32_t)__half_as_ushort(vin_lo) << 16),
+                               (uint32_t)__half_as_ushort(vz_hi) | ((uint32_t)__half_as_ushort(vz_lo) << 16), 0u, 0u);
+                        sts128(ax + N * 16, 0u, 0u, 0u, 0u);
                     }
                 }
                 fence_async_smem();
@@ -1312,15 +1321,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         // columns of S(j), free once P(j) is complete, and goes first because the softmax two tiles ahead
         // waits for it while nobody waits for the accumulator.
         constexpr uint32_t IDESC_S = instr_desc(TC_M, N, 0);
-        constexpr uint32_t IDESC_O = instr_desc(TC_M, D, 1);
-        constexpr uint32_t IDESC_AUX = instr_desc(TC_M, 16, 0);
+        constexpr uint32_t IDESC_O = instr_desc(TC_M, D + 16, 1);     // output columns and normaliser columns in one product
         bool ok = true;
         // descriptors differ from their stage base only in the start-address field (bits 0-13, 16-byte units)
         const uint64_t qd0 = smem_desc(smem_u32(smem + P::OFF_Q), 16, 1024);
         const uint64_t kd0 = smem_desc(smem_u32(smem + P::OFF_K), 16, 1024);
         const uint64_t pd0 = smem_desc(smem_u32(smem + P::OFF_P), 16, 1024);
-        const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), N * 128, 1024);
-        const uint64_t ad0 = smem_desc(smem_u32(smem + P::OFF_AUX), 16, 1024);
+        // unswizzled MN-major: leading offset = between key blocks (8 keys), stride offset = between 8-column blocks
+        const uint64_t vd0 = smem_desc(smem_u32(smem + P::OFF_V), 128, N * 16, 0u);
         // S = Q K^T of tile j.  exact-code K: Q_hi K [+ Q_lo K]; dequantised K: Q_hi K_hi + Q_hi K_lo [+ Q_lo K_hi]
         auto issue_qk = [&](int j) -> bool {
             const int s = j & 1;
@@ -1349,17 +1357,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             tc_commit(&bar_s[s]);
             return true;
         };
-        // O_half += P V and (sum_k P / V-scale, sum_k P * V zero-point) += P aux, 16 keys per step; the first
-        // half of a tile's keys goes to accumulator 0, the second half to accumulator 1
-        // MMAs of one shape are issued together: a change of instruction shape between consecutive MMAs costs the tensor
-        // pipe a few hundred cycles, so a tile's O products go first and its normaliser products after them.
-        bool o_live[2] = {false, false}, x_live[2] = {false, false};
+        // (O_half | sum_k P / V-scale, sum_k P * V zero-point) += P (V | normaliser columns), 16 keys per step; the first half
+        // of a tile's keys goes to accumulator 0, the second half to accumulator 1
+        bool o_live[2] = {false, false};
         auto issue_pv = [&](int j) {
             const int s = j & 1;
             const int ksteps = (tile_n(j) + 15) >> 4;                // P columns / V rows past the keys are never read
-            const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::KV_BYTES) >> 4);
-            const uint64_t ad = ad0 + (uint64_t)((s * P::AUX_BYTES) >> 4);
-            // rolled on purpose: the loops are short-lived code that every CTA has to fetch again
+            const uint64_t pd = pd0 + (uint64_t)(((s & (P::PST - 1)) * P::P_BYTES) >> 4), vd = vd0 + (uint64_t)((s * P::V_BYTES) >> 4);
+            // rolled on purpose: the loop is short-lived code that every CTA has to fetch again
             uint64_t pk = pd, vk = vd;
 #pragma unroll 1
             for (int kk = 0; kk < ksteps; ++kk) {
@@ -1368,20 +1373,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 // half of the keys may first appear in a later tile than the first half)
                 tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS, pk, vk, IDESC_O, o_live[hf] ? 1u : 0u);
                 o_live[hf] = true;
-                // next 16 keys: 32 bytes further in the K-major tile (a new 64-key block every fourth step), 16 rows in V
+                // next 16 keys: 32 bytes further in the K-major P tile (a new 64-key block every fourth step), two key blocks in V
                 pk += ((kk & 3) == 3) ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
-                vk += (uint64_t)(2048 >> 4);
-            }
-            uint64_t ak = ad;
-            pk = pd;
-#pragma unroll 1
-            for (int kk = 0; kk < ksteps; ++kk) {
-                const int hf = kk >= N / 32 ? 1 : 0;
-                tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS + D, pk, ak, IDESC_AUX, x_live[hf] ? 1u : 0u);
-                x_live[hf] = true;
-                const bool wrap = (kk & 3) == 3;
-                pk += wrap ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
-                ak += wrap ? (uint64_t)((2048 - 96) >> 4) : 2u;
+                vk += (uint64_t)(256 >> 4);
             }
             tc_commit(&bar_pv[s]);
         };
