@@ -122,6 +122,27 @@ int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int
                     const varq_tensor_t* codes, const varq_qparams_t* p,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Producer side of the attention hook in one pass over the fresh q, k, v (views of the fused QKV activation):
+ *   q_out = q / max(||q||_2, eps) * scale_mul[h],   k_out = k / max(||k||_2, eps)          (fp32, norms over head_dim)
+ * and, in the same read, the min / max statistics of k_out and of v for groupings that are shared over batch and
+ * tokens (per-dim, per-step, per-tensor), folded into `k_stats` / `v_stats` (varq_quant_workspace_bytes() bytes each,
+ * cleared by this call).  varq_quant_pack_prestats then quantizes from those tables without a statistics pass of its
+ * own, so K and V are read once less.  scale_mul may be NULL (= 1); v_in / the statistics pointers may be NULL.
+ * Replaces the L2-normalisation of VAR/models/basic_var.py:137-141 and Infinity/infinity/models/basic.py:316-320
+ * and the first pass of VAR_Q._compute_scale (VAR_Q/quant.py:112-116). */
+int varq_qk_norm_stats(const varq_tensor_t* q_in, const varq_tensor_t* k_in, const varq_tensor_t* v_in,
+                       int32_t B, int32_t L, int32_t H, int32_t D, const float* scale_mul, float eps,
+                       const varq_tensor_t* q_out, const varq_tensor_t* k_out,
+                       const varq_qparams_t* k_grouping, void* k_stats,
+                       const varq_qparams_t* v_grouping, void* v_stats, void* stream);
+
+/* varq_quant_pack with the statistics table already filled by varq_qk_norm_stats (same grouping, same tensor):
+ * scale / zero-point computation, rounding and packing only.  Same results as varq_quant_pack. */
+int varq_quant_pack_prestats(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D,
+                             int32_t bits, int32_t store_bits, float eps,
+                             const varq_tensor_t* codes, const varq_qparams_t* p,
+                             void* stats, size_t stats_bytes, void* stream);
+
 /* varq_quant_pack for callers that may not allocate device memory and have no scratch
  * buffer to lend.  No counterpart in the reference.
  *

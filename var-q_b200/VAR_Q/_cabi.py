@@ -22,6 +22,7 @@ SYMBOLS = (
     "varq_quant_workspace_bytes", "varq_quant_pack", "varq_quant_pack_static",
     "varq_quant_static_scratch_bytes", "varq_unpack_dequant",
     "varq_attn_workspace_bytes", "varq_attn_fwd", "varq_attn_force_path",
+    "varq_qk_norm_stats", "varq_quant_pack_prestats",
 )
 
 
@@ -62,6 +63,10 @@ def _declare(lib):
     lib.varq_quant_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, Q]
     lib.varq_quant_pack.restype = i32
     lib.varq_quant_pack.argtypes = [T, i32, i32, i32, i32, i32, i32, f32, T, Q, vp, sz, vp]
+    lib.varq_quant_pack_prestats.restype = i32
+    lib.varq_quant_pack_prestats.argtypes = [T, i32, i32, i32, i32, i32, i32, f32, T, Q, vp, sz, vp]
+    lib.varq_qk_norm_stats.restype = i32
+    lib.varq_qk_norm_stats.argtypes = [T, T, T, i32, i32, i32, i32, vp, f32, T, T, Q, vp, Q, vp, vp]
     lib.varq_quant_pack_static.restype = i32
     lib.varq_quant_pack_static.argtypes = [T, i32, i32, i32, i32, i32, i32, f32, T, Q, vp]
     lib.varq_quant_static_scratch_bytes.restype = sz

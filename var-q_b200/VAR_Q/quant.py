@@ -196,19 +196,33 @@ class VAR_Q:
         return _cabi.tensor_desc(t.data_ptr(), _cabi.DTYPES[t.dtype], sb, sl, sh)
 
     # ------------------------------------------------------------------ kernels
-    def _quantize_into(self, item: torch.Tensor, codes, s_tbl, z_tbl, tok0: int, row0: int):
+    def _quantize_into(self, item: torch.Tensor, codes, s_tbl, z_tbl, tok0: int, row0: int, stats=None):
         B, H, D = self._shape
         n = item.size(self.dim_cat)
         lib = _cabi.lib()
         grouping = self._param_desc(s_tbl, z_tbl, row0, D)
-        ws_bytes = lib.varq_quant_workspace_bytes(B, n, H, D, _cabi.DTYPES[item.dtype], self.store_bits, grouping)
-        ws = _cabi.workspace(item.device, ws_bytes) if ws_bytes else None
         with torch.cuda.device(item.device):
-            rc = lib.varq_quant_pack(
-                self._item_desc(item), B, n, H, D, self.quant_bits, self.store_bits, float(self.eps),
-                self._codes_desc(codes, tok0), grouping,
-                ws.data_ptr() if ws is not None else None, ws_bytes, _cabi.stream_ptr(item.device))
+            if stats is not None:      # the statistics pass already ran inside the fused producer kernel
+                rc = lib.varq_quant_pack_prestats(
+                    self._item_desc(item), B, n, H, D, self.quant_bits, self.store_bits, float(self.eps),
+                    self._codes_desc(codes, tok0), grouping, stats.data_ptr(), stats.numel() * stats.element_size(),
+                    _cabi.stream_ptr(item.device))
+            else:
+                ws_bytes = lib.varq_quant_workspace_bytes(B, n, H, D, _cabi.DTYPES[item.dtype], self.store_bits, grouping)
+                ws = _cabi.workspace(item.device, ws_bytes) if ws_bytes else None
+                rc = lib.varq_quant_pack(
+                    self._item_desc(item), B, n, H, D, self.quant_bits, self.store_bits, float(self.eps),
+                    self._codes_desc(codes, tok0), grouping,
+                    ws.data_ptr() if ws is not None else None, ws_bytes, _cabi.stream_ptr(item.device))
         _cabi.check(rc)
+
+    def column_grouping(self, D: int):
+        """The grouping descriptor of this quantizer if its statistics are shared over batch and tokens of a step and the
+        step is quantized on its own (per-dim, per-step modes) -- the case the fused producer kernel can prepare -- else None."""
+        share_b, share_l, share_h, group = self._grouping(D)
+        if not (share_b and share_l) or self.quant_method in _REQUANT:
+            return None
+        return _cabi.QParams(None, None if self.symmetric else 1, None, 0, 0, 0, 1, 1, 1, int(share_h), group)
 
     def _dequant(self, codes, s_tbl, z_tbl, tok0: int, n: int, row0: int, rot, out_dtype=torch.float32):
         B, H, D = self._shape
@@ -228,8 +242,9 @@ class VAR_Q:
         return out
 
     # ------------------------------------------------------------------ reference API
-    def quant(self, item: torch.Tensor):
-        """Quantize one appended step (VAR_Q/quant.py:140-177)."""
+    def quant(self, item: torch.Tensor, stats: Optional[torch.Tensor] = None):
+        """Quantize one appended step (VAR_Q/quant.py:140-177).  `stats`: statistics table of this very tensor as left by
+        ``varq_qk_norm_stats`` (see ``column_grouping``); the kernel then skips its own statistics pass."""
         _cabi.require_cuda(item, "item")
         if item.dim() != 4:
             raise ValueError(f"[VAR-Q]: item must be 4-D ({self._fmt}), got {tuple(item.shape)}")
@@ -260,7 +275,7 @@ class VAR_Q:
         else:
             rows = 1 if share_l else n
             self._ensure(item, n, rows, B, H, D)
-            self._quantize_into(item, self._codes, self._scale_tbl, self._zp_tbl, self._n_tokens, self._n_rows)
+            self._quantize_into(item, self._codes, self._scale_tbl, self._zp_tbl, self._n_tokens, self._n_rows, stats)
             if share_l:
                 self._row_of_token[self._n_tokens:self._n_tokens + n] = self._n_rows
                 self._row_begin[self._n_rows + 1:self._n_rows + 2].fill_(self._n_tokens + n)   # entry n_rows already holds n_tokens
@@ -316,9 +331,9 @@ class VAR_Q:
         return self.dequant_all()
 
     # ------------------------------------------------------------------ fused path
-    def append(self, item: torch.Tensor):
+    def append(self, item: torch.Tensor, stats: Optional[torch.Tensor] = None):
         """quant + cache without materialising the dequantised cache."""
-        self.quant(item)
+        self.quant(item, stats)
         self.cache()
 
     @property

@@ -55,11 +55,15 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     a.v16 = words_aligned16(v_codes, wv);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     a.splits = 1; a.tiles_per_split = 0; a.n_qtiles = 1; a.ws = reinterpret_cast<float*>(workspace);
-    // up to 16 queries stay on the CUDA-core kernels (memory-bound); the rest goes to the tensor cores
+    // The CUDA-core streaming kernel is memory-bound only while its arithmetic (queries x keys x head_dim on the FMA pipe)
+    // stays below the time to stream the packed cache: up to 4 queries at any cache length, and the 1-16-query first scales
+    // of a schedule, whose caches are a few hundred tokens at most.  Everything else goes to the tensor cores, where a
+    // 128-row tile with few live rows still finishes a long cache sooner.
     const int force = __atomic_load_n(&g_forced_path, __ATOMIC_RELAXED);
-    const bool want_tc = force ? (force == VARQ_ATTN_PATH_TC) : (Lq > 16);
+    const bool small_q = Lq <= 4 || (Lq <= 16 && Lk <= 256);
+    const bool want_tc = force ? (force == VARQ_ATTN_PATH_TC) : !small_q;
     if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, (cudaStream_t)stream);
-    const bool want_stream = force ? (force == VARQ_ATTN_PATH_STREAM) : (Lq <= 16);
+    const bool want_stream = force ? (force == VARQ_ATTN_PATH_STREAM) : small_q;
     if (want_stream && attn_stream_eligible(a, kb, vb)) return attn_stream_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
 }

@@ -289,6 +289,24 @@ __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// Walk over the (key, 16-byte item) pairs of a tile, `nthr` threads abreast.  KEYMAJ: neighbouring lanes take neighbouring
+// keys of one item column, which makes the 16-byte operand-tile stores of a quarter-warp land in one 128-byte line
+// (several stores per item, so they outweigh the strided read of the packed row); otherwise neighbouring lanes take the
+// items of one key (contiguous packed reads).
+template <bool KEYMAJ> struct ItemWalk {
+    int key, item, rows, nthr, ipr, ishift, it;
+    __device__ __forceinline__ void init(int ptid, int rows_, int ipr_, int nthr_) {
+        rows = rows_; nthr = nthr_; ipr = ipr_; ishift = __ffs(ipr_) - 1; it = ptid;
+        if (KEYMAJ) { item = ptid / rows_; key = ptid - item * rows_; }
+        else { key = ptid >> ishift; item = ptid & (ipr_ - 1); }
+    }
+    __device__ __forceinline__ bool more() const { return KEYMAJ ? item < ipr : key < rows; }
+    __device__ __forceinline__ void next() {
+        if (KEYMAJ) { key += nthr; while (key >= rows) { key -= rows; ++item; } }
+        else { it += nthr; key = it >> ishift; item = it & (ipr - 1); }
+    }
+};
+
 // Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS, bool VL = false>      // VL: the unswizzled V layout
 __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
@@ -297,12 +315,10 @@ __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* pac
     if (rows < 0) rows = N;
     constexpr int VPW = 32 / BITS;            // codes per word
     constexpr int HW = VPW / 2;               // 32-bit half2 registers per word
-    const int ipr = W >> 2;                   // 16-byte items per key row
-    const int ishift = __ffs(ipr) - 1;
-    const int items = rows * ipr;
+    ItemWalk<(BITS < 8)> wk;      // measured: 8-bit rows (64 or 128 bytes per key) convert faster item by item
 #pragma unroll 1
-    for (int it = ptid; it < items; it += nthr) {
-        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
         uint4 pk = make_uint4(0u, 0u, 0u, 0u);
         uint32_t h[4 * HW];
         if (key < n_valid) {
@@ -508,10 +524,10 @@ template <int BITS>
 __device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed, const uint2* par,
                                               int n_valid, int N, int W, int ptid, int g_shift, int grp_shift) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
-    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = N * ipr;
+    ItemWalk<false> wk;      // the items of a key share a parameter record: neighbouring lanes read it together
 #pragma unroll 1
-    for (int it = ptid; it < items; it += 128) {
-        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+    for (wk.init(ptid, N, W >> 2, 128); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
         uint32_t hi[4 * HW], lo[4 * HW];
         if (key < n_valid) {
             const uint4 pk = lds128(packed + key * W + wi);
@@ -552,10 +568,10 @@ template <int BITS>
 __device__ __noinline__ void group_tile(unsigned char* tile, const uint32_t* packed, const uint2* par, int n_valid, int N, int W,
                                         int ptid, int nthr, int rows, int g_shift, int grp_shift) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
-    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = rows * ipr;
+    ItemWalk<false> wk;
 #pragma unroll 1
-    for (int it = ptid; it < items; it += nthr) {
-        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
         uint32_t h[4 * HW];
         if (key < n_valid) {
             const uint4 pk = lds128(packed + key * W + wi);
@@ -589,10 +605,10 @@ template <int BITS>
 __device__ __noinline__ void perdim_tile(unsigned char* tile, const uint32_t* packed, const __half* s_h, const __half* sl_h, const __half* zb_h,
                                          int n_valid, int N, int W, int ptid, int nthr, int rows) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
-    const int ipr = W >> 2, ishift = __ffs(ipr) - 1, items = rows * ipr;
+    ItemWalk<true> wk;
 #pragma unroll 1
-    for (int it = ptid; it < items; it += nthr) {
-        const int key = it >> ishift, wi = (it & (ipr - 1)) << 2;
+    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
         const int d0 = wi * VPW;
         uint32_t h[4 * HW];
         if (key < n_valid) {
@@ -1287,7 +1303,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 for (int i = 0; i < KPT; ++i) {
                     const int kt = ptid + i * TC_VPROD;
                     if (kt < N) {
-                        const float vin = TC_AUX_DOWN / fmaxf(vs[i], TC_VS_MIN), vzd = vz[i] * TC_ZP_DOWN;
+                        const float vin = TC_AUX_DOWN * __frcp_rn(fmaxf(vs[i], TC_VS_MIN)), vzd = vz[i] * TC_ZP_DOWN;
                         const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
                         const __half vin_lo = __float2half_rn(vin - __half2float(vin_hi)), vz_lo = __float2half_rn(vzd - __half2float(vz_hi));
                         unsigned char* ax = tv + vtile_off(kt, D, N);
@@ -1335,31 +1351,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             if (!mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31)) return false;
             tc_fence_after();
             const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
-            // the k-step loop stays rolled (descriptors advance by increments): unrolled, its 64-bit descriptor constants
-            // spill, and the issuing thread is the one thread everybody waits for
-            uint64_t qk = qd0, kk_d = kd;
-#pragma unroll 1
-            for (int kk = 0; kk < D / 16; ++kk) {
+            bool first = true;
 #pragma unroll
-                for (int qi = 0; qi < NQ; ++qi) {
+            for (int qi = 0; qi < NQ; ++qi) {
 #pragma unroll
-                    for (int ki = 0; ki < P::KT; ++ki) {
-                        if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
-                        tc_mma_f16(tmem_base + P::COL_S + s * N, qk + (uint64_t)((qi * P::Q_BYTES) >> 4),
-                                   kk_d + (uint64_t)((ki * P::KV_BYTES) >> 4), IDESC_S, (kk == 0 && qi == 0 && ki == 0) ? 0u : 1u);
+                for (int ki = 0; ki < P::KT; ++ki) {
+                    if (qi == 1 && ki == 1) continue;     // lo x lo is below fp32 resolution
+                    const uint64_t qd = qd0 + (uint64_t)((qi * P::Q_BYTES) >> 4), kdk = kd + (uint64_t)((ki * P::KV_BYTES) >> 4);
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        tc_mma_f16(tmem_base + P::COL_S + s * N, qd + (uint64_t)(((kk >> 2) * (TC_M * 128) + (kk & 3) * 32) >> 4),
+                                   kdk + (uint64_t)(((kk >> 2) * (N * 128) + (kk & 3) * 32) >> 4), IDESC_S, first ? 0u : 1u);
+                        first = false;
                     }
                 }
-                // next 16 head_dim values: 32 bytes further inside the 64-column block, a new block every fourth step
-                const bool wrap = (kk & 3) == 3;
-                qk += wrap ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
-                kk_d += wrap ? (uint64_t)((N * 128 - 96) >> 4) : 2u;
             }
             tc_commit(&bar_s[s]);
             return true;
         };
         // (O_half | sum_k P / V-scale, sum_k P * V zero-point) += P (V | normaliser columns), 16 keys per step; the first half
         // of a tile's keys goes to accumulator 0, the second half to accumulator 1
-        bool o_live[2] = {false, false};
+        bool live0 = false, live1 = false;        // scalars, not an array: a runtime-indexed array would live in local memory
         auto issue_pv = [&](int j) {
             const int s = j & 1;
             const int ksteps = (tile_n(j) + 15) >> 4;                // P columns / V rows past the keys are never read
@@ -1371,8 +1383,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                 const int hf = kk >= N / 32 ? 1 : 0;
                 // the first product into an accumulator overwrites it (with tiles cut at step boundaries the second
                 // half of the keys may first appear in a later tile than the first half)
-                tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS, pk, vk, IDESC_O, o_live[hf] ? 1u : 0u);
-                o_live[hf] = true;
+                tc_mma_f16(tmem_base + P::COL_O + hf * P::ACC_COLS, pk, vk, IDESC_O, (hf ? live1 : live0) ? 1u : 0u);
+                if (hf) live1 = true; else live0 = true;
                 // next 16 keys: 32 bytes further in the K-major P tile (a new 64-key block every fourth step), two key blocks in V
                 pk += ((kk & 3) == 3) ? (uint64_t)((TC_M * 128 - 96) >> 4) : 2u;
                 vk += (uint64_t)(256 >> 4);

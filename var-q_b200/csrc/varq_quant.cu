@@ -63,21 +63,27 @@ __device__ __forceinline__ void params_from_range(const Range& r, int bits, bool
 // once in 10^4 elements) the exact division decides.  Rounding is done by adding 1.5 * 2^23, which
 // also leaves the two's-complement code in the low mantissa bits.
 struct GroupQ {
-    float scale, zp, rcp_lo, rcp_hi, y_min, y_max;
+    float scale, zp, rcp_lo, rcp_hi;
 };
 constexpr float Q_MAGIC = 12582912.0f;
-__device__ __forceinline__ GroupQ make_group_q(float scale, float zp, int bits) {
+__device__ __forceinline__ GroupQ make_group_q(float scale, float zp) {
     GroupQ g;
     const float rcp = __frcp_rn(scale);
     g.scale = scale; g.zp = zp;
     g.rcp_lo = rcp * (1.0f - 4.76837158e-7f);
     g.rcp_hi = rcp * (1.0f + 4.76837158e-7f);
-    g.y_min = Q_MAGIC - (float)(1 << (bits - 1));
-    g.y_max = Q_MAGIC + (float)((1 << (bits - 1)) - 1);
     return g;
 }
+// The code range depends on the bit width only: Q_MAGIC + bound_min / bound_max, one pair per thread.
+struct CodeRange { float y_min, y_max; };
+__device__ __forceinline__ CodeRange make_code_range(int bits) {
+    CodeRange r;
+    r.y_min = Q_MAGIC - (float)(1 << (bits - 1));
+    r.y_max = Q_MAGIC + (float)((1 << (bits - 1)) - 1);
+    return r;
+}
 template <bool SYM>
-__device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g) {
+__device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g, const CodeRange& cr) {
     float y = fmaf(x, g.rcp_hi, Q_MAGIC);
     const float y2 = fmaf(x, g.rcp_lo, Q_MAGIC);
     bool slow = y != y2;
@@ -85,16 +91,16 @@ __device__ __forceinline__ uint32_t quant_code(float x, const GroupQ& g) {
     if (slow) {
         float k = rintf(__fdiv_rn(x, g.scale));
         if (!SYM) k = __fadd_rn(k, g.zp);
-        y = fminf(fmaxf(k, g.y_min - Q_MAGIC), g.y_max - Q_MAGIC) + Q_MAGIC;
+        y = fminf(fmaxf(k, cr.y_min - Q_MAGIC), cr.y_max - Q_MAGIC) + Q_MAGIC;
     } else if (!SYM) {
         y = ((y - Q_MAGIC) + g.zp) + Q_MAGIC;                           // integers below 2^23: exact
     }
-    y = fminf(fmaxf(y, g.y_min), g.y_max);
+    y = fminf(fmaxf(y, cr.y_min), cr.y_max);
     return __float_as_uint(y);
 }
 
-__device__ __forceinline__ uint32_t quant_code_rt(float x, const GroupQ& g, bool sym) {
-    return sym ? quant_code<true>(x, g) : quant_code<false>(x, g);
+__device__ __forceinline__ uint32_t quant_code_rt(float x, const GroupQ& g, const CodeRange& cr, bool sym) {
+    return sym ? quant_code<true>(x, g, cr) : quant_code<false>(x, g, cr);
 }
 
 // =====================================================================================
@@ -224,16 +230,17 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(QuantArgs a, RowPlan pl
 
     // ---- quantize, pack, store
     float scale = 0.f, zp = 0.f;
-    GroupQ gq = make_group_q(1.f, 0.f, a.bits);
-    if (a.share_b) { params_from_range(rg[0], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp, a.bits); }
+    const CodeRange cr = make_code_range(a.bits);
+    GroupQ gq = make_group_q(1.f, 0.f);
+    if (a.share_b) { params_from_range(rg[0], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp); }
 #pragma unroll
     for (int k = 0; k < NVMAX; ++k) {
         if (xoff[k] < 0) continue;
-        if (!a.share_b) { params_from_range(rg[k], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp, a.bits); }
+        if (!a.share_b) { params_from_range(rg[k], a.bits, sym, a.eps, scale, zp); gq = make_group_q(scale, zp); }
         uint32_t word = 0;
 #pragma unroll
         for (int j = 0; j < VPW; ++j) {
-            word |= (quant_code_rt(v[k][j], gq, sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+            word |= (quant_code_rt(v[k][j], gq, cr, sym) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
         }
         a.codes[vb[k] * a.cs_b + vl[k] * a.cs_l + vh[k] * a.cs_h + w] = (int32_t)word;
         const bool writer = (d0 % a.group) == 0 && (a.share_b ? (vb[k] == 0) : true);
@@ -311,14 +318,15 @@ __global__ void __launch_bounds__(256) quant_rows_lean_kernel(QuantArgs a, LeanP
     }
     float scale, zp;
     params_from_range(rg, a.bits, SYM, a.eps, scale, zp);
-    const GroupQ gq = make_group_q(scale, zp, a.bits);
+    const GroupQ gq = make_group_q(scale, zp);
+    const CodeRange cr = make_code_range(a.bits);
     int32_t* cp = a.codes + c0;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
         uint32_t word = 0;
 #pragma unroll
         for (int j = 0; j < VPW; ++j)
-            word |= (quant_code<SYM>(v[k][j], gq) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+            word |= (quant_code<SYM>(v[k][j], gq, cr) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
         cp[k * pl.cs_bstep] = (int32_t)word;
     }
     if (bl == 0 && (d0 % a.group) == 0) {
@@ -509,11 +517,10 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
     }
 }
 
-template <typename T, int STORE_BITS, bool VEC>
+template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __global__ void __launch_bounds__(256) quant_stats_kernel(QuantArgs a, int iters) {
     extern __shared__ uint32_t s_fold[];            // [blockDim.x * VPW][2] when rows are folded in the block
-    if (a.symmetric) quant_stats_body<T, STORE_BITS, VEC, true>(a, iters, s_fold);
-    else             quant_stats_body<T, STORE_BITS, VEC, false>(a, iters, s_fold);
+    quant_stats_body<T, STORE_BITS, VEC, SYM>(a, iters, s_fold);
 }
 
 // Between the two passes: one thread per group turns its (max, min) entry into the scale and zero-point that
@@ -540,7 +547,7 @@ template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
     constexpr int UN = TAB_UNROLL;
-    constexpr bool REPL = VPW <= 4;      // replicating shared parameters costs 6 registers per value: only for short words
+    constexpr bool REPL = VPW <= 4;      // replicating shared parameters costs 4 registers per value: only for short words
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     if (cs >= a.H * a.words) return;
     const int h = cs / a.words, w = cs % a.words;
@@ -554,6 +561,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     int32_t* ccol = a.codes + h * a.cs_h + w;
 
     GroupQ gq[VPW];
+    const CodeRange cr = make_code_range(a.bits);
     const long long p_h = h * a.ps_h;
     auto fetch = [&](int b, int l) {
         const long long p_row = (a.share_b ? 0 : b) * a.ps_b + (a.share_l ? 0 : l) * a.ps_r + (a.share_h ? 0 : p_h);
@@ -562,7 +570,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
             if (j >= np) break;
             const int d = min(d0 + j, a.D - 1);
             const long long pi = p_row + (long long)(d / a.group) * a.ps_g;
-            gq[j] = make_group_q(a.scale[pi], SYM ? 0.0f : a.zp[pi], a.bits);
+            gq[j] = make_group_q(a.scale[pi], SYM ? 0.0f : a.zp[pi]);
         }
         if (REPL && uniform) {   // one group for all of the thread's values: replicate, so the inner loop never selects
 #pragma unroll
@@ -595,7 +603,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
             for (int j = 0; j < VPW; ++j) {
                 if (j < n_valid) {
                     const GroupQ g = (REPL || !uniform) ? gq[j] : gq[0];
-                    word |= (quant_code<SYM>(v[u][j], g) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
+                    word |= (quant_code<SYM>(v[u][j], g, cr) & ((1u << STORE_BITS) - 1u)) << (j * STORE_BITS);
                 }
             }
             ccol[co[u]] = (int32_t)word;
@@ -603,10 +611,9 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     }
 }
 
-template <typename T, int STORE_BITS, bool VEC>
+template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters) {
-    if (a.symmetric) quant_apply_body<T, STORE_BITS, VEC, true>(a, iters);
-    else             quant_apply_body<T, STORE_BITS, VEC, false>(a, iters);
+    quant_apply_body<T, STORE_BITS, VEC, SYM>(a, iters);
 }
 
 // ---------------------------------------------------------------- host side
@@ -684,14 +691,15 @@ static bool plan_lean(const QuantArgs& a, int vpw, bool vec, const RowPlan& rp, 
     return true;
 }
 
+// `have_stats`: the statistics table in `ws` is already filled (by varq_qk_norm_stats); only finalize + apply run.
 template <typename T, int SB>
-static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes, cudaStream_t st) {
+static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes, cudaStream_t st, bool have_stats = false) {
     QuantArgs a = a0;
     constexpr int VPW = 32 / SB;
     RowPlan pl;
     int threads = 0;
     size_t smem = 0;
-    if (plan_rows(a, VPW, vec, pl, threads, smem) && threads >= 32) {
+    if (!have_stats && plan_rows(a, VPW, vec, pl, threads, smem) && threads >= 32) {
         const long long per_cta = a.share_b ? pl.ngr : (long long)pl.ngr * pl.nv;
         const long long blocks = (pl.n_gr + per_cta - 1) / per_cta;
         if (blocks > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack: tensor too large");
@@ -715,7 +723,7 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     if (!ws || ws_bytes < need)
         return fail(VARQ_ERR_WORKSPACE, "varq_quant_pack: workspace of %zu bytes needed, %zu given", need, ws_bytes);
     a.stats = reinterpret_cast<uint32_t*>(ws);
-    VARQ_CUDA_TRY(cudaMemsetAsync(a.stats, 0, need, st));
+    if (!have_stats) VARQ_CUDA_TRY(cudaMemsetAsync(a.stats, 0, need, st));
     const int cols = a.H * a.words;
     int tx = 32;
     while (tx < cols && tx < 256) tx <<= 1;
@@ -745,26 +753,26 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
     const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
     const unsigned fin_blocks = (unsigned)((groups + 255) / 256);
-    if (vec) {
-        quant_stats_kernel<T, SB, true><<<grid, block, fold, st>>>(a, iters);
-        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);
-        quant_apply_kernel<T, SB, true><<<grid, block, 0, st>>>(a, iters);
-    } else {
-        quant_stats_kernel<T, SB, false><<<grid, block, fold, st>>>(a, iters);
-        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);
-        quant_apply_kernel<T, SB, false><<<grid, block, 0, st>>>(a, iters);
-    }
+#define VARQ_TWO_PASS(VEC_, SYM_)                                                  \
+    do {                                                                            \
+        if (!have_stats) quant_stats_kernel<T, SB, VEC_, SYM_><<<grid, block, fold, st>>>(a, iters); \
+        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);               \
+        quant_apply_kernel<T, SB, VEC_, SYM_><<<grid, block, 0, st>>>(a, iters);    \
+    } while (0)
+    if (vec) { if (a.symmetric) VARQ_TWO_PASS(true, true); else VARQ_TWO_PASS(true, false); }
+    else     { if (a.symmetric) VARQ_TWO_PASS(false, true); else VARQ_TWO_PASS(false, false); }
+#undef VARQ_TWO_PASS
     VARQ_CUDA_TRY(cudaGetLastError());
-    count_launches(3);
+    count_launches(have_stats ? 2 : 3);
     return VARQ_OK;
 }
 
 template <int SB>
-static int dispatch_quant(const QuantArgs& a, int dtype, bool vec, void* ws, size_t wsb, cudaStream_t st) {
+static int dispatch_quant(const QuantArgs& a, int dtype, bool vec, void* ws, size_t wsb, cudaStream_t st, bool have_stats = false) {
     switch (dtype) {
-        case VARQ_F32: return launch_quant<float, SB>(a, vec, ws, wsb, st);
-        case VARQ_F16: return launch_quant<__half, SB>(a, vec, ws, wsb, st);
-        default:       return launch_quant<__nv_bfloat16, SB>(a, vec, ws, wsb, st);
+        case VARQ_F32: return launch_quant<float, SB>(a, vec, ws, wsb, st, have_stats);
+        case VARQ_F16: return launch_quant<__half, SB>(a, vec, ws, wsb, st, have_stats);
+        default:       return launch_quant<__nv_bfloat16, SB>(a, vec, ws, wsb, st, have_stats);
     }
 }
 
@@ -789,19 +797,21 @@ extern "C" size_t varq_quant_workspace_bytes(int32_t B, int32_t L, int32_t H, in
     return (size_t)groups * 2 * sizeof(uint32_t);
 }
 
-extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D, int32_t bits,
-                               int32_t store_bits, float eps, const varq_tensor_t* codes, const varq_qparams_t* p,
-                               void* workspace, size_t workspace_bytes, void* stream) {
-    if (!x || !codes || !p) return fail(VARQ_ERR_ARG, "varq_quant_pack: null descriptor");
-    if (bits < 2 || bits > 8) return fail(VARQ_ERR_ARG, "varq_quant_pack: bits must be in [2, 8] (got %d)", bits);
+static int quant_pack_impl(const char* fn, const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D, int32_t bits,
+                           int32_t store_bits, float eps, const varq_tensor_t* codes, const varq_qparams_t* p, void* workspace,
+                           size_t workspace_bytes, void* stream, bool have_stats) {
+    if (!x || !codes || !p) return fail(VARQ_ERR_ARG, "%s: null descriptor", fn);
+    if (bits < 2 || bits > 8) return fail(VARQ_ERR_ARG, "%s: bits must be in [2, 8] (got %d)", fn, bits);
     if (store_bits != 2 && store_bits != 4 && store_bits != 8)
-        return fail(VARQ_ERR_ARG, "varq_quant_pack: store_bits must be 2, 4 or 8 (got %d)", store_bits);
-    if (store_bits < bits) return fail(VARQ_ERR_ARG, "varq_quant_pack: store_bits %d cannot hold %d-bit codes", store_bits, bits);
-    if (B < 0 || L < 0 || H < 0 || D <= 0) return fail(VARQ_ERR_ARG, "varq_quant_pack: bad shape (%d,%d,%d,%d)", B, L, H, D);
-    if (!dtype_ok(x->dtype)) return fail(VARQ_ERR_ARG, "varq_quant_pack: bad input dtype %d", x->dtype);
-    if (int rc = check_grouping("varq_quant_pack", p, D)) return rc;
+        return fail(VARQ_ERR_ARG, "%s: store_bits must be 2, 4 or 8 (got %d)", fn, store_bits);
+    if (store_bits < bits) return fail(VARQ_ERR_ARG, "%s: store_bits %d cannot hold %d-bit codes", fn, store_bits, bits);
+    if (B < 0 || L < 0 || H < 0 || D <= 0) return fail(VARQ_ERR_ARG, "%s: bad shape (%d,%d,%d,%d)", fn, B, L, H, D);
+    if (!dtype_ok(x->dtype)) return fail(VARQ_ERR_ARG, "%s: bad input dtype %d", fn, x->dtype);
+    if (int rc = check_grouping(fn, p, D)) return rc;
+    if (have_stats && !(p->share_b && p->share_l))
+        return fail(VARQ_ERR_UNSUPPORTED, "%s: ready-made statistics exist for groupings shared over batch and tokens only", fn);
     if ((long long)B * L * H == 0) return VARQ_OK;
-    if (!x->ptr || !codes->ptr || !p->scale) return fail(VARQ_ERR_ARG, "varq_quant_pack: null pointer");
+    if (!x->ptr || !codes->ptr || !p->scale) return fail(VARQ_ERR_ARG, "%s: null pointer", fn);
 
     const int vpw = 32 / store_bits;
     QuantArgs a;
@@ -817,9 +827,21 @@ extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int
     a.stats = nullptr;
     const bool vec = vec_ok(x, D, vpw);
     cudaStream_t st = (cudaStream_t)stream;
-    if (store_bits == 8) return dispatch_quant<8>(a, x->dtype, vec, workspace, workspace_bytes, st);
-    if (store_bits == 4) return dispatch_quant<4>(a, x->dtype, vec, workspace, workspace_bytes, st);
-    return dispatch_quant<2>(a, x->dtype, vec, workspace, workspace_bytes, st);
+    if (store_bits == 8) return dispatch_quant<8>(a, x->dtype, vec, workspace, workspace_bytes, st, have_stats);
+    if (store_bits == 4) return dispatch_quant<4>(a, x->dtype, vec, workspace, workspace_bytes, st, have_stats);
+    return dispatch_quant<2>(a, x->dtype, vec, workspace, workspace_bytes, st, have_stats);
+}
+
+extern "C" int varq_quant_pack(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D, int32_t bits,
+                               int32_t store_bits, float eps, const varq_tensor_t* codes, const varq_qparams_t* p,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    return quant_pack_impl("varq_quant_pack", x, B, L, H, D, bits, store_bits, eps, codes, p, workspace, workspace_bytes, stream, false);
+}
+
+extern "C" int varq_quant_pack_prestats(const varq_tensor_t* x, int32_t B, int32_t L, int32_t H, int32_t D, int32_t bits,
+                                        int32_t store_bits, float eps, const varq_tensor_t* codes, const varq_qparams_t* p,
+                                        void* stats, size_t stats_bytes, void* stream) {
+    return quant_pack_impl("varq_quant_pack_prestats", x, B, L, H, D, bits, store_bits, eps, codes, p, stats, stats_bytes, stream, true);
 }
 
 // =====================================================================================
