@@ -472,6 +472,42 @@ def gpu_eager_baseline(w, device, inputs):
             "what": "reference algorithm as eager torch ops + SDPA (bf16) on this GPU, one block timed and scaled by the depth; informational"}
 
 
+def loop_harness(device, images=32):
+    """The hook between GEMMs: a stand-in VAR-d16 block loop (random-init LayerNorm / QKV / proj / MLP layers of the model's
+    shapes around the installed packed-cache attention), launched from Python and replayed as one CUDA graph."""
+    from VAR_Q.harness import StandInVAR
+    model = StandInVAR().to(device).to(torch.bfloat16)
+    maps = model.token_maps(images, device)
+    for _ in range(2):
+        model.generate(maps)
+    torch.cuda.synchronize()
+
+    def timed(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    eager_ms = timed(lambda: model.generate(maps), 3)
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        model.generate(maps)
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        model.generate(maps)
+    graph.replay()
+    torch.cuda.synchronize()
+    graph_ms = timed(graph.replay, 5)
+    return {"loop_images_per_s": images / (graph_ms * 1e-3), "loop_ms_graph": graph_ms, "loop_ms_python_launched": eager_ms,
+            "what": "stand-in VAR-d16 block loop (random-init torch LayerNorm / QKV / proj / MLP in bf16 around the installed "
+                    "packed-cache attention, INT8 per-head), 10 scales x 16 blocks, B=32 (+CFG); no tokenizer, sampling or image decode"}
+
+
 def load_traffic(kernel_key):
     """DRAM bytes per unit for a kernel from the ncu capture recorded in profiles/ncu_traffic.json, valid only while
     the kernel's source file is the one the capture was taken on."""
@@ -713,6 +749,10 @@ def run_ours(args):
                          "gpu_launches": r["launches"], "workload": wo["desc"]}
                 if name == "var_d16":
                     rec_o["gpu_eager_baseline"] = gpu_eager_baseline(wo, device, r["inputs"])
+                    del r
+                    torch.cuda.empty_cache()
+                    rec_o["loop"] = loop_harness(device, wo["images"])
+                    r = None
                 others[name] = rec_o
                 del r
                 torch.cuda.empty_cache()

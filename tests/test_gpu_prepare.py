@@ -143,3 +143,26 @@ def test_install_takes_over_a_var_shaped_module_under_autocast(method, bits, l2)
     assert m._varq_kv is None
     with pytest.raises(AssertionError):
         m(torch.randn(1, 2, width, device=DEV), None)            # not caching: the original forward is called
+
+
+def test_stand_in_block_loop_runs_eagerly_and_as_a_cuda_graph():
+    from VAR_Q.harness import StandInVAR
+    torch.manual_seed(3)
+    model = StandInVAR(depth=2, width=128, heads=2, patch_nums=(1, 2, 3, 5), q_bits=4, quant_method="G_SCALE_HEAD_DIM",
+                       k_kwargs=dict(symmetric=False)).to(DEV).to(torch.bfloat16)
+    maps = model.token_maps(3, DEV)
+    eager = model.generate(maps).clone()
+    assert eager.shape == (6, 25, 128) and torch.isfinite(eager.float()).all()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model.generate(maps)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.generate(maps)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    assert _cabi.device_status() == 0
