@@ -5,25 +5,27 @@ import pytest
 
 from VAR_Q.config_loader import VARQConfig, load_varq_config
 
-CFG_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "var-q_b200", "VAR_Q")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CFG_DIR = os.path.join(ROOT, "var-q_b200", "VAR_Q")                  # this build's own configurations
+REF_CFG_DIR = os.path.join(ROOT, "tests", "golden", "reference_configs")   # the reference's shipped files, as fixtures
 
 
 def test_reference_shaped_files_load():
-    c = load_varq_config(os.path.join(CFG_DIR, "VAR-VAR_Q-8.json"))
+    c = load_varq_config(os.path.join(REF_CFG_DIR, "VAR-VAR_Q-8.json"))
     assert c.is_var_model() and not c.is_infinity_model()
     q = c.get_quantization_config()
     assert (q["enable"], q["q_bits"], q["quant_method"], q["qkv_format"]) == (True, 8, "G_SCALE_HEAD_DIM", "BLHc")
     assert c.get_checkpoint_paths(16)[1].endswith("var_d16.pth")
     assert c.get_inference_config()["top_k"] == 600 and c.get_batch_processing_config()["batch_size"] == 50
-    i = load_varq_config(os.path.join(CFG_DIR, "Infinity-VAR_Q-8.json"))
+    i = load_varq_config(os.path.join(REF_CFG_DIR, "Infinity-VAR_Q-8.json"))
     assert i.is_infinity_model() and i.get_checkpoint_paths()[1].endswith("infinity_2b_reg.pth")
-    raw = load_varq_config(os.path.join(CFG_DIR, "VAR-raw.json"))
+    raw = load_varq_config(os.path.join(REF_CFG_DIR, "VAR-raw.json"))
     assert raw.get_quantizer_kwargs("k") is None
     assert c.get_device() in ("cpu", "cuda")
 
 
 def test_sections_are_copies_and_updates_merge(tmp_path):
-    c = VARQConfig(os.path.join(CFG_DIR, "VAR-VAR_Q-8.json"))
+    c = VARQConfig(os.path.join(REF_CFG_DIR, "VAR-VAR_Q-8.json"))
     c.get_quantization_config()["q_bits"] = 2
     assert c.get_quantization_config()["q_bits"] == 8
     c.update_config({"quantization": {"q_bits": 4}, "extra": {"a": {"b": 1}}})

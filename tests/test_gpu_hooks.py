@@ -65,7 +65,7 @@ def test_from_config_resolves_per_tensor_settings():
     q = torch.randn(2, 5, 3, 64, device=DEV)
     out = kv.step(q, torch.randn(2, 5, 3, 64, device=DEV), torch.randn(2, 5, 3, 64, device=DEV), 0.125)
     assert out.shape == (2, 5, 3, 64) and torch.isfinite(out).all()
-    raw = load_varq_config(os.path.join(CFG_DIR, "VAR-raw.json"))
+    raw = load_varq_config(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_configs", "VAR-raw.json"))
     assert LayerKV.from_config(raw) is None
     kv.set_format("BHLc")
     assert kv.k_quant.dim_cat == 2

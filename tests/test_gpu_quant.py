@@ -279,3 +279,32 @@ def test_batch_shared_groups_register_resident_path(B, bits, symmetric, group):
                  symmetric=symmetric, group_size=group)
     run_pair("BLHc", "G_TOKEN_HEAD", bits, (3, 4), B=B, H=2, c=128, dtype=torch.float16, seed=B, strided=True,
              symmetric=symmetric, group_size=group)
+
+
+# ------------------------------------------------------------------ compact cache save / load, statistics
+@pytest.mark.parametrize("mode,kw", [("G_TOKEN_HEAD", dict(symmetric=False, group_size=32)), ("G_SCALE_HEAD_DIM", {}), ("G_HEAD_DIM", {})])
+def test_cache_round_trips_through_save_and_load(mode, kw, tmp_path):
+    dut, ref = run_pair("BLHc", mode, 4, (1, 4, 9), B=3, H=2, c=64, seed=11, **kw)
+    path = str(tmp_path / "cache.pt")
+    dut.save(path)
+    other = VAR_Q(quant_bits=4, qkv_format="BLHc", quant_method=mode, **kw).load(path)
+    assert other.n_tokens == 14 and bits_equal(other.cached_item, ref.cached_item) and bits_equal(other.cached_scale, ref.cached_scale)
+    assert bits_equal(other.dequant_all(), ref.dequant_all())
+    x = O.synthetic_kv((3, 16, 2, 64), "BLHc", 99)
+    assert bits_equal(other.use_var_q(x.to(DEV)), ref.use_var_q(x))           # appending to a restored cache continues it
+    with pytest.raises(ValueError):
+        VAR_Q(quant_bits=8, qkv_format="BLHc", quant_method=mode, **kw).load(path)
+
+
+def test_debug_statistics_rows_and_csv(tmp_path):
+    q = VAR_Q(quant_bits=4, qkv_format="BLHc", quant_method="G_TOKEN_HEAD", blk_idx=5, debug=True)
+    for si, n in enumerate((2, 7)):
+        x = O.synthetic_kv((2, n, 3, 64), "BLHc", 40 + si).to(DEV)
+        q.use_var_q(x)
+    rows = q.debug_rows
+    assert len(rows) == 2 and rows[1]["cached_tokens"] == 9 and rows[0]["blk_idx"] == 5
+    assert 0.0 < rows[0]["rel_l2_error"] < 0.5 and rows[0]["max_abs_error"] <= rows[0]["scale_max"] * 0.5 * 1.0001
+    path = str(tmp_path / "stats.csv")
+    q.write_statistics_csv(path)
+    lines = open(path).read().strip().splitlines()
+    assert len(lines) == 3 and lines[0].startswith("blk_idx,step_tokens,cached_tokens")

@@ -224,10 +224,12 @@ class VAR_Q:
             return None
         return _cabi.QParams(None, None if self.symmetric else 1, None, 0, 0, 0, 1, 1, 1, int(share_h), group)
 
-    def _dequant(self, codes, s_tbl, z_tbl, tok0: int, n: int, row0: int, rot, out_dtype=torch.float32):
+    def _dequant(self, codes, s_tbl, z_tbl, tok0: int, n: int, row0: int, rot, out_dtype=torch.float32, out=None):
         B, H, D = self._shape
         shape = (B, n, H, D) if self._fmt == 'BLHc' else (B, H, n, D)
-        out = torch.empty(shape, dtype=out_dtype, device=codes.device)
+        if out is None:
+            out = torch.empty(shape, dtype=out_dtype, device=codes.device)
+        assert tuple(out.shape) == shape and out.stride(-1) == 1
         p = self._param_desc(s_tbl, z_tbl, row0, D, rot)
         if rot is None and p.share_l:
             p.stride_r = 0          # one row describes every token of the range
@@ -263,7 +265,12 @@ class VAR_Q:
         share_l = _GROUPING[self.quant_method][0]
         if self.quant_method in _REQUANT and self._n_tokens:
             # whole-cache modes: dequantise what is cached, join the new step, re-quantise everything
-            full = torch.cat([self.dequant_all(), item.to(torch.float32)], dim=self.dim_cat)
+            # the dequantised cache is written straight into the head of the joint buffer and the new step behind it: no
+            # concatenation pass over the whole cache (the reference does dequant_all + torch.cat, VAR_Q/quant.py:149-154)
+            L0 = self._n_tokens
+            full = torch.empty((B, L0 + n, H, D) if self._fmt == 'BLHc' else (B, H, L0 + n, D), dtype=torch.float32, device=item.device)
+            self._dequant(self._codes, self._scale_tbl, self._zp_tbl, 0, L0, 0, self._row_of_token, out=full.narrow(self.dim_cat, 0, L0))
+            full.narrow(self.dim_cat, L0, n).copy_(item)
             self._ensure(full, n, 0, B, H, D)
             if self._codes_next is None:
                 self._codes_next = torch.empty_like(self._codes)
@@ -328,6 +335,8 @@ class VAR_Q:
         """quant -> cache -> dequant_all (VAR_Q/quant.py:227-230)."""
         self.quant(item)
         self.cache()
+        if self.debug:
+            self.__dict__.setdefault('debug_rows', []).append(self.step_statistics(item))
         return self.dequant_all()
 
     # ------------------------------------------------------------------ fused path
@@ -335,6 +344,8 @@ class VAR_Q:
         """quant + cache without materialising the dequantised cache."""
         self.quant(item, stats)
         self.cache()
+        if self.debug:
+            self.__dict__.setdefault('debug_rows', []).append(self.step_statistics(item))
 
     @property
     def n_tokens(self) -> int:
@@ -347,6 +358,95 @@ class VAR_Q:
         if self._row_of_token is not None:
             p.row_begin, p.n_rows = self._row_begin.data_ptr(), self._n_rows
         return self._codes_desc(self._codes, 0), p
+
+    # ------------------------------------------------------------------ compact cache: save / load
+    def state_dict(self) -> Dict[str, object]:
+        """The committed cache in its compact on-device format: packed codes ``[B, H, L, words]``, the parameter tables
+        ``[nB, nH, rows, groups]`` (one row per token, or per appended step with ``row_of_token`` / ``row_begin``), and the
+        settings needed to read them.  The reference keeps scales materialised along L (VAR_Q/quant.py:180-201) and has no
+        serialised form; this one is about ``bits / 8`` bytes per cached element."""
+        if self._pending is not None:
+            raise ValueError("[VAR-Q]: commit the quantized step with cache() before saving")
+        n, r = self._n_tokens, self._n_rows
+        per_step = self._row_of_token is not None
+        return {
+            'format': 'varq_b200.cache.v1',
+            'settings': dict(quant_bits=self.quant_bits, qkv_format=self._fmt, quant_method=self.quant_method,
+                             pack_to_int32=self.pack_to_int32, eps=self.eps, symmetric=self.symmetric,
+                             group_size=self.group_size, reduce_batch=self.reduce_batch),
+            'shape': self._shape, 'n_tokens': n, 'n_rows': r, 'pack_meta': self._pack_meta, 'last': self._last,
+            'codes': None if n == 0 else self._codes[:, :, :n].clone(),
+            'scale': None if n == 0 else self._scale_tbl[:, :, :r].clone(),
+            'zp': None if (n == 0 or self._zp_tbl is None) else self._zp_tbl[:, :, :r].clone(),
+            'row_of_token': self._row_of_token[:n].clone() if (per_step and n) else None,
+            'row_begin': self._row_begin[:r + 1].clone() if (per_step and n) else None,
+        }
+
+    def load_state_dict(self, state: Dict[str, object], device=None):
+        """Restore a cache written by ``state_dict`` (settings must match this quantizer's)."""
+        if state.get('format') != 'varq_b200.cache.v1':
+            raise ValueError("[VAR-Q]: not a varq_b200 cache")
+        mine = dict(quant_bits=self.quant_bits, qkv_format=self._fmt, quant_method=self.quant_method,
+                    pack_to_int32=self.pack_to_int32, eps=self.eps, symmetric=self.symmetric,
+                    group_size=self.group_size, reduce_batch=self.reduce_batch)
+        theirs = dict(state['settings'])
+        theirs['qkv_format'] = mine['qkv_format']        # the layout of the items is a property of the caller, not of the cache
+        if theirs != mine:
+            raise ValueError(f"[VAR-Q]: cache was written with {state['settings']}, this quantizer has {mine}")
+        self._codes = self._codes_next = self._scale_tbl = self._zp_tbl = self._scale_next = self._zp_next = None
+        self._row_of_token = self._row_begin = None
+        self._shape, self._n_tokens, self._n_rows, self._pending = None, 0, 0, None
+        self._pack_meta, self._last = state['pack_meta'], state['last']
+        n, r = int(state['n_tokens']), int(state['n_rows'])
+        if n == 0:
+            return self
+        codes = state['codes']
+        dev = torch.device(device) if device is not None else codes.device
+        _cabi.require_cuda(torch.empty(0, device=dev), "the cache device")
+        B, H, D = state['shape']
+        probe = torch.empty((B, 1, H, D) if self._fmt == 'BLHc' else (B, H, 1, D), device=dev)
+        self._ensure(probe, n, r, B, H, D)               # allocates tables of at least n tokens / r rows
+        self._codes[:, :, :n] = codes.to(dev)
+        self._scale_tbl[:, :, :r] = state['scale'].to(dev)
+        if self._zp_tbl is not None:
+            self._zp_tbl[:, :, :r] = state['zp'].to(dev)
+        if self._row_of_token is not None:
+            self._row_of_token[:n] = state['row_of_token'].to(dev)
+            self._row_begin[:r + 1] = state['row_begin'].to(dev)
+        self._n_tokens, self._n_rows = n, r
+        return self
+
+    def save(self, path: str):
+        torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.state_dict().items()}, path)
+
+    def load(self, path: str, device='cuda'):
+        return self.load_state_dict(torch.load(path, map_location='cpu', weights_only=False), device=device)
+
+    # ------------------------------------------------------------------ range / error statistics (debug=True)
+    def step_statistics(self, item: torch.Tensor) -> Dict[str, float]:
+        """Range and quantization error of the step quantized last against its input ``item``: the figures the reference's
+        README lists as "range stats / L2 error" (README.md:11) and its code never computes (``debug`` is stored and unused,
+        VAR_Q/quant.py:61,73).  Plain torch on the device; not part of the hot path."""
+        deq = self.dequant_current()
+        x = item.to(torch.float32)
+        err = deq - x
+        sc = self.scale
+        return {
+            'blk_idx': int(self.cur_blk_idx), 'step_tokens': int(item.size(self.dim_cat)), 'cached_tokens': int(self._n_tokens),
+            'x_min': float(x.min()), 'x_max': float(x.max()), 'x_abs_mean': float(x.abs().mean()),
+            'scale_min': float(sc.min()), 'scale_max': float(sc.max()),
+            'rel_l2_error': float(err.norm() / x.norm().clamp_min(1e-30)), 'max_abs_error': float(err.abs().max()),
+        }
+
+    def write_statistics_csv(self, path: str):
+        """Write the rows collected by ``use_var_q`` / ``append`` while ``debug=True`` as CSV."""
+        import csv
+        rows = getattr(self, 'debug_rows', [])
+        with open(path, 'w', newline='') as f:
+            if rows:
+                w = csv.DictWriter(f, fieldnames=list(rows[0].keys()))
+                w.writeheader()
+                w.writerows(rows)
 
     # ------------------------------------------------------------------ reference-shaped views
     def _ref_codes(self, codes: torch.Tensor, tok0: int, n: int) -> torch.Tensor:

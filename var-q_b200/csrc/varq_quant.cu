@@ -382,7 +382,9 @@ template <bool SYM> __device__ __forceinline__ Range frange_ord(const FRange& r)
     return o;
 }
 
-constexpr int TAB_UNROLL = 4;   // independent row loads in flight per thread
+// independent row loads in flight per thread: 32 values whatever the word width (8 rows of 4, 4 of 8, 2 of 16), the
+// budget that keeps the single-pass kernel at four CTAs per SM
+constexpr int tab_unroll(int vpw) { return 32 / vpw < 2 ? 2 : 32 / vpw; }
 
 template <typename T, int STORE_BITS, bool VEC, bool SYM>
 __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, uint32_t* s_fold) {
@@ -407,6 +409,7 @@ __device__ __forceinline__ void quant_stats_body(const QuantArgs& a, int iters, 
     const int l0 = (int)ri.l;                       // this thread's token index when it is fixed
     if (!row_dep) {
         // ---- statistics do not depend on the row: accumulate in registers, several loads in flight
+        constexpr int TAB_UNROLL = tab_unroll(VPW);
         for (int it = 0; it < iters; it += TAB_UNROLL) {
             float v[TAB_UNROLL][VPW];
             bool ok[TAB_UNROLL];
@@ -543,10 +546,10 @@ __global__ void __launch_bounds__(256) quant_finalize_kernel(QuantArgs a, long l
     if (!a.symmetric) a.zp[pi] = zp;
 }
 
-template <typename T, int STORE_BITS, bool VEC, bool SYM>
+template <typename T, int STORE_BITS, bool VEC, bool SYM, bool ROWDEP>
 __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) {
     constexpr int VPW = 32 / STORE_BITS;
-    constexpr int UN = TAB_UNROLL;
+    constexpr int UN = VPW == 4 ? 4 : tab_unroll(VPW);     // 8-bit words: four rows keep the kernel at three CTAs per SM
     constexpr bool REPL = VPW <= 4;      // replicating shared parameters costs 4 registers per value: only for short words
     const int cs = blockIdx.x * blockDim.x + threadIdx.x;
     if (cs >= a.H * a.words) return;
@@ -554,7 +557,7 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     const int d0 = w * VPW;
     const int n_valid = min(VPW, a.D - d0);
     const bool uniform = (a.group % VPW) == 0;
-    const bool row_dep = !(a.share_b && (a.share_l || a.l_fixed));
+    constexpr bool row_dep = ROWDEP;      // parameters change with the (sample, token) row; otherwise they are fetched once
     const unsigned R = (unsigned)a.B * (unsigned)a.L;
     const int np = uniform ? 1 : VPW;
     const T* xcol = reinterpret_cast<const T*>(a.x) + h * a.xs_h + d0;
@@ -589,15 +592,15 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
             ok[u] = it + u < iters && ri.r < R;
-            rb[u] = ri.b; rl[u] = ri.l; co[u] = ri.coff;
+            if (ROWDEP) { rb[u] = ri.b; rl[u] = ri.l; }
+            co[u] = ri.coff;
             if (ok[u]) load_vals<T, VPW, VEC>(xcol + ri.xoff, v[u], n_valid);
             ri.next();
         }
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
             if (!ok[u]) continue;
-            const int b = (int)rb[u], l = (int)rl[u];
-            if (row_dep) fetch(b, l);
+            if (ROWDEP) fetch((int)rb[u], (int)rl[u]);
             uint32_t word = 0;
 #pragma unroll
             for (int j = 0; j < VPW; ++j) {
@@ -611,9 +614,9 @@ __device__ __forceinline__ void quant_apply_body(const QuantArgs& a, int iters) 
     }
 }
 
-template <typename T, int STORE_BITS, bool VEC, bool SYM>
+template <typename T, int STORE_BITS, bool VEC, bool SYM, bool ROWDEP>
 __global__ void __launch_bounds__(256) quant_apply_kernel(QuantArgs a, int iters) {
-    quant_apply_body<T, STORE_BITS, VEC, SYM>(a, iters);
+    quant_apply_body<T, STORE_BITS, VEC, SYM, ROWDEP>(a, iters);
 }
 
 // ---------------------------------------------------------------- host side
@@ -753,11 +756,13 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
     const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
     const unsigned fin_blocks = (unsigned)((groups + 255) / 256);
+    const bool row_dep = !(a.share_b && (a.share_l || a.l_fixed));
 #define VARQ_TWO_PASS(VEC_, SYM_)                                                  \
     do {                                                                            \
         if (!have_stats) quant_stats_kernel<T, SB, VEC_, SYM_><<<grid, block, fold, st>>>(a, iters); \
         quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);               \
-        quant_apply_kernel<T, SB, VEC_, SYM_><<<grid, block, 0, st>>>(a, iters);    \
+        if (row_dep) quant_apply_kernel<T, SB, VEC_, SYM_, true><<<grid, block, 0, st>>>(a, iters);    \
+        else         quant_apply_kernel<T, SB, VEC_, SYM_, false><<<grid, block, 0, st>>>(a, iters);   \
     } while (0)
     if (vec) { if (a.symmetric) VARQ_TWO_PASS(true, true); else VARQ_TWO_PASS(true, false); }
     else     { if (a.symmetric) VARQ_TWO_PASS(false, true); else VARQ_TWO_PASS(false, false); }
