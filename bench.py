@@ -508,9 +508,11 @@ def loop_harness(device, images=32):
                     "packed-cache attention, INT8 per-head), 10 scales x 16 blocks, B=32 (+CFG); no tokenizer, sampling or image decode"}
 
 
-def load_traffic(kernel_key):
-    """DRAM bytes per unit for a kernel from the ncu capture recorded in profiles/ncu_traffic.json, valid only while
-    the kernel's source file is the one the capture was taken on."""
+def load_traffic(kernel_key, launch_bytes):
+    """DRAM bytes of one launch of the dominant kernel, from the ncu capture recorded in profiles/ncu_traffic.json: the
+    capture ran a smaller case of the same kernel and settings (the full launch is too large to capture), so its DRAM
+    bytes are scaled by the ratio of the algorithmic bytes of the two launches.  Valid only while the kernel's source
+    file is the one the capture was taken on."""
     path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
     if not os.path.exists(path):
         return None, "no ncu capture recorded"
@@ -520,8 +522,10 @@ def load_traffic(kernel_key):
     src = os.path.join(ROOT, rec["source"])
     sha = hashlib.sha256(open(src, "rb").read()).hexdigest()[:16] if os.path.exists(src) else None
     if sha != rec["source_sha256_16"]:
-        return None, f"ncu capture in {rec['summary']} predates the current {rec['source']}"
-    return rec, f"ncu capture summarised in {rec['summary']} (same {rec['source']}), scaled by {rec['unit']}"
+        return None, f"the ncu capture in {rec['summary']} predates the current {rec['source']}"
+    ratio = rec["dram_bytes"] / rec["algorithmic_bytes_of_capture"]
+    return int(ratio * launch_bytes), (f"ncu capture of a smaller launch ({rec['capture']}; {rec['dram_bytes']} DRAM bytes for "
+                                       f"{rec['algorithmic_bytes_of_capture']} algorithmic bytes, summary in {rec['summary']}), scaled by algorithmic bytes")
 
 
 def run_workload(w, device, args, lib, barrier, steps, warmup, want_probe=True, graph_mode=True):
@@ -705,17 +709,14 @@ def run_ours(args):
             roof = roof_entry(f"attn[scale {si}: l={lq}, cached={lk}]", w["desc"].split(":")[0], top_ms, peaks,
                               nbytes=attn_bytes(w, b2, lq, lk), flops=attn_flops(w, b2, lq, lk), kernels=top_launches)
             key = "attn_tc_kernel" if lq > 16 else "attn_stream_kernel"
-            units, unit_name = b2 * w["heads"], "(sample, head) pairs"
         else:
             bits, mode, kw = w["k"] if kind == "quant_k" else w["v"]
             n_el = b2 * lq * w["heads"] * w["head_dim"]
             groups = lq * w["heads"] * (w["head_dim"] // kw["group_size"] if kw.get("group_size") else 1) if mode == "G_TOKEN_HEAD" else w["heads"] * w["head_dim"]
             roof = roof_entry(f"{kind}[scale {si}: l={lq}]", w["desc"].split(":")[0], top_ms, peaks,
                               nbytes=quant_bytes(n_el, 4 if kind == "quant_k" else 2, bits, groups, kw.get("symmetric", True)), kernels=top_launches)
-            key, units, unit_name = "quant", n_el, "elements"
-        trec, tsrc = load_traffic(f"{key}:{args.workload}")
-        roof["traffic"] = None if trec is None else int(trec["dram_bytes_per_unit"] * units)
-        roof["traffic_source"] = tsrc
+            key = "quant"
+        roof["traffic"], roof["traffic_source"] = load_traffic(f"{key}:{args.workload}", roof["algorithmic_bytes"])
         roof["share_of_step"] = share[top] / sum(share.values())
         roof["timing"] = "CUDA events around back-to-back launches of this call on the step's own state"
         line = {
