@@ -735,9 +735,24 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     const int ty = per_token ? 1 : 256 / tx;
     const long long R = (long long)a.B * a.L;
     const int gx = (cols + tx - 1) / tx;
-    long long gy = (R + ty - 1) / ty;
     if (R >= 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_quant_pack: batch x tokens exceeds 2^31");
-    const long long cap = ((long long)sm_count() * 4 + gx - 1) / gx;   // ~4 CTAs of 256 threads per SM
+    // the two kernels of this call, by vector width, symmetry and whether parameters change with the (sample, token) row
+    using KernelFn = void (*)(QuantArgs, int);
+    const bool row_dep = !(a.share_b && (a.share_l || per_token));
+    KernelFn stats_fn, apply_fn;
+#define VARQ_PICK(VEC_, SYM_)                                                                           \
+    do {                                                                                                 \
+        stats_fn = quant_stats_kernel<T, SB, VEC_, SYM_>;                                                \
+        apply_fn = row_dep ? (KernelFn)quant_apply_kernel<T, SB, VEC_, SYM_, true> : (KernelFn)quant_apply_kernel<T, SB, VEC_, SYM_, false>; \
+    } while (0)
+    if (vec) { if (a.symmetric) VARQ_PICK(true, true); else VARQ_PICK(true, false); }
+    else     { if (a.symmetric) VARQ_PICK(false, true); else VARQ_PICK(false, false); }
+#undef VARQ_PICK
+    // the grid is one wave of the heavier (apply) kernel: as many CTAs per SM as its registers allow, no tail wave
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, apply_fn, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 2;
+    long long gy = (R + ty - 1) / ty;
+    const long long cap = ((long long)sm_count() * per_sm + gx - 1) / gx;
     if (gy > cap) gy = cap;
     if (gy < 1) gy = 1;
     if (gy > 65535) gy = 65535;
@@ -756,17 +771,9 @@ static int launch_quant(const QuantArgs& a0, bool vec, void* ws, size_t ws_bytes
     dim3 block(tx, ty), grid(gx, (unsigned)gy);
     const size_t fold = ty > 1 ? (size_t)tx * VPW * 2 * sizeof(uint32_t) : 0;
     const unsigned fin_blocks = (unsigned)((groups + 255) / 256);
-    const bool row_dep = !(a.share_b && (a.share_l || a.l_fixed));
-#define VARQ_TWO_PASS(VEC_, SYM_)                                                  \
-    do {                                                                            \
-        if (!have_stats) quant_stats_kernel<T, SB, VEC_, SYM_><<<grid, block, fold, st>>>(a, iters); \
-        quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);               \
-        if (row_dep) quant_apply_kernel<T, SB, VEC_, SYM_, true><<<grid, block, 0, st>>>(a, iters);    \
-        else         quant_apply_kernel<T, SB, VEC_, SYM_, false><<<grid, block, 0, st>>>(a, iters);   \
-    } while (0)
-    if (vec) { if (a.symmetric) VARQ_TWO_PASS(true, true); else VARQ_TWO_PASS(true, false); }
-    else     { if (a.symmetric) VARQ_TWO_PASS(false, true); else VARQ_TWO_PASS(false, false); }
-#undef VARQ_TWO_PASS
+    if (!have_stats) stats_fn<<<grid, block, fold, st>>>(a, iters);
+    quant_finalize_kernel<<<fin_blocks, 256, 0, st>>>(a, groups);
+    apply_fn<<<grid, block, 0, st>>>(a, iters);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(have_stats ? 2 : 3);
     return VARQ_OK;
