@@ -877,6 +877,14 @@ def run_case(name):
         qshape = (B, lq, H, D) if fmt == "BLHc" else (B, H, lq, D)
         q = torch.nn.functional.normalize(torch.randn(qshape, generator=g, device=dev), dim=-1) * Q_GAIN
         fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
+    elif name == "stream":    # one query per (sample, head) over 10 521 packed tokens, INT4 K and V, head_dim 128: 1.4 GB of codes
+        B, H, D, lk = 64, 16, 128, 10521
+        kq, vq = VAR_Q(4, "BHLc", "G_TOKEN_HEAD", max_tokens=lk), VAR_Q(4, "BHLc", "G_TOKEN_HEAD", max_tokens=lk)
+        kq.append(torch.nn.functional.normalize(torch.randn((B, H, lk, D), generator=g, device=dev), dim=-1))
+        vq.append(torch.randn((B, H, lk, D), generator=g, device=dev).to(torch.bfloat16))
+        q = (torch.nn.functional.normalize(torch.randn((B, H, 1, D), generator=g, device=dev), dim=-1) * Q_GAIN).to(torch.bfloat16)
+        fn = lambda: attend_cached(q, kq, vq, 1.0, out_dtype=torch.bfloat16)
+        nbytes = 2 * B * H * lk * D // 2
     else:                     # "quant": 252 MB of fp32 K, per-head INT8, batch-shared groups; "quant2": per-dim groups (two passes)
         x = torch.randn((128, 256, 30, 64), generator=g, device=dev)
         qz = VAR_Q(8, "BLHc", "G_TOKEN_HEAD" if name == "quant" else "G_SCALE_HEAD_DIM", max_tokens=256)
@@ -903,7 +911,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the isolated dequant-attention sweep")
     ap.add_argument("--quick", action="store_true", help="headline measurement only (no per-kernel rooflines, sweep, other workloads, CPU leg)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--case", choices=("attn", "attn_perdim", "attn_group", "quant", "quant2"),
+    ap.add_argument("--case", choices=("attn", "attn_perdim", "attn_group", "stream", "quant", "quant2"),
                     help="run one kernel on a small case and exit (profiling aid)")
     args = ap.parse_args()
     if args.case:

@@ -24,28 +24,42 @@ constexpr int ST_SHORT_KEYS = 64;  // ... and one-warp CTAs below this many keys
 constexpr int ST_QT = 4;          // query slots (matches the merge kernel's record layout)
 constexpr int ST_UNROLL = 4;      // warp steps in flight
 
-__device__ __forceinline__ uint32_t st_h2_sub(uint32_t a, uint32_t b) {
-    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-    return *reinterpret_cast<uint32_t*>(&r);
+// ---- packed codes -> fp32 without conversion instructions.  A byte u placed in the low byte of 0x4B000000 is the float
+// 2^23 + u; codes are biased to unsigned bytes first, so one byte permute per value builds 2^23 + BIAS + code and one packed
+// fp32 add per two values removes 2^23 + BIAS.  Arithmetic then runs on packed fp32 pairs (two FMAs per instruction).
+__device__ __forceinline__ void st_fma2(float& d0, float& d1, float a0, float a1, float b0, float b1) {      // d += a * b, pairwise
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rd, {%0, %1};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rd;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
-__device__ __forceinline__ void st_bytes_to_f4(uint32_t u, uint32_t bias, float* f) {
-    const uint32_t h01 = st_h2_sub(__byte_perm(u, 0x64646464u, 0x4140), bias);
-    const uint32_t h23 = st_h2_sub(__byte_perm(u, 0x64646464u, 0x4342), bias);
-    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h01));
-    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&h23));
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+__device__ __forceinline__ void st_add2(float& d0, float& d1, float b) {                                     // d += b, pairwise
+    asm("{\n\t.reg .b64 rb, rd;\n\tmov.b64 rb, {%2, %2};\n\tmov.b64 rd, {%0, %1};\n\t"
+        "add.rn.f32x2 rd, rd, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(b));
+}
+__device__ __forceinline__ float st_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// byte `B` of u -> 2^23 + that byte, as a float
+template <int B> __device__ __forceinline__ float st_byte_f(uint32_t u) { return __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540 + B)); }
+__device__ __forceinline__ void st_bytes_f4(uint32_t u, float* f) {
+    f[0] = st_byte_f<0>(u); f[1] = st_byte_f<1>(u); f[2] = st_byte_f<2>(u); f[3] = st_byte_f<3>(u);
 }
 
-// 16 codes of `BITS` bits (little-endian fields) -> 16 floats holding the signed integers
+// 16 codes of `BITS` bits (little-endian fields) -> 16 floats holding the signed integers, in field order
 template <int BITS> struct StCodes;
 template <> struct StCodes<8> {
     using Raw = uint4;
     static __device__ __forceinline__ Raw load(const int32_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
     static __device__ __forceinline__ void cvt(const Raw& r, float* f) {
-        st_bytes_to_f4(r.x ^ 0x80808080u, 0x64806480u, f);
-        st_bytes_to_f4(r.y ^ 0x80808080u, 0x64806480u, f + 4);
-        st_bytes_to_f4(r.z ^ 0x80808080u, 0x64806480u, f + 8);
-        st_bytes_to_f4(r.w ^ 0x80808080u, 0x64806480u, f + 12);
+        st_bytes_f4(r.x ^ 0x80808080u, f);
+        st_bytes_f4(r.y ^ 0x80808080u, f + 4);
+        st_bytes_f4(r.z ^ 0x80808080u, f + 8);
+        st_bytes_f4(r.w ^ 0x80808080u, f + 12);
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) st_add2(f[j], f[j + 1], -(8388608.f + 128.f));
     }
 };
 template <> struct StCodes<4> {
@@ -53,25 +67,29 @@ template <> struct StCodes<4> {
     static __device__ __forceinline__ Raw load(const int32_t* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
     static __device__ __forceinline__ void word(uint32_t w, float* f) {
         const uint32_t x = w ^ 0x88888888u;
-        const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-        st_bytes_to_f4(__byte_perm(lo, hi, 0x5140), 0x64086408u, f);
-        st_bytes_to_f4(__byte_perm(lo, hi, 0x7362), 0x64086408u, f + 4);
+        const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;      // fields 0,2,4,6 / 1,3,5,7
+        f[0] = st_byte_f<0>(lo); f[1] = st_byte_f<0>(hi); f[2] = st_byte_f<1>(lo); f[3] = st_byte_f<1>(hi);
+        f[4] = st_byte_f<2>(lo); f[5] = st_byte_f<2>(hi); f[6] = st_byte_f<3>(lo); f[7] = st_byte_f<3>(hi);
     }
-    static __device__ __forceinline__ void cvt(const Raw& r, float* f) { word(r.x, f); word(r.y, f + 8); }
+    static __device__ __forceinline__ void cvt(const Raw& r, float* f) {
+        word(r.x, f); word(r.y, f + 8);
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) st_add2(f[j], f[j + 1], -(8388608.f + 8.f));
+    }
 };
 template <> struct StCodes<2> {
     using Raw = uint32_t;
     static __device__ __forceinline__ Raw load(const int32_t* p) { return (uint32_t)__ldg(p); }
     static __device__ __forceinline__ void cvt(const Raw& w, float* f) {
         const uint32_t x = w ^ 0xAAAAAAAAu;
-        const uint32_t t0 = x & 0x03030303u, t1 = (x >> 2) & 0x03030303u;
-        const uint32_t t2 = (x >> 4) & 0x03030303u, t3 = (x >> 6) & 0x03030303u;
-        const uint32_t a = __byte_perm(t0, t1, 0x5140), b = __byte_perm(t2, t3, 0x5140);
-        const uint32_t c = __byte_perm(t0, t1, 0x7362), d = __byte_perm(t2, t3, 0x7362);
-        st_bytes_to_f4(__byte_perm(a, b, 0x5410), 0x64026402u, f);
-        st_bytes_to_f4(__byte_perm(a, b, 0x7632), 0x64026402u, f + 4);
-        st_bytes_to_f4(__byte_perm(c, d, 0x5410), 0x64026402u, f + 8);
-        st_bytes_to_f4(__byte_perm(c, d, 0x7632), 0x64026402u, f + 12);
+        const uint32_t t0 = x & 0x03030303u, t1 = (x >> 2) & 0x03030303u;       // fields 0,4,8,12 / 1,5,9,13
+        const uint32_t t2 = (x >> 4) & 0x03030303u, t3 = (x >> 6) & 0x03030303u; // fields 2,6,10,14 / 3,7,11,15
+        f[0] = st_byte_f<0>(t0); f[1] = st_byte_f<0>(t1); f[2] = st_byte_f<0>(t2); f[3] = st_byte_f<0>(t3);
+        f[4] = st_byte_f<1>(t0); f[5] = st_byte_f<1>(t1); f[6] = st_byte_f<1>(t2); f[7] = st_byte_f<1>(t3);
+        f[8] = st_byte_f<2>(t0); f[9] = st_byte_f<2>(t1); f[10] = st_byte_f<2>(t2); f[11] = st_byte_f<2>(t3);
+        f[12] = st_byte_f<3>(t0); f[13] = st_byte_f<3>(t1); f[14] = st_byte_f<3>(t2); f[15] = st_byte_f<3>(t3);
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) st_add2(f[j], f[j + 1], -(8388608.f + 2.f));
     }
 };
 
@@ -162,11 +180,11 @@ __global__ void __launch_bounds__(WARPS * 32) attn_stream_kernel(AttnArgs a, int
             float s[QT];
 #pragma unroll
             for (int qi = 0; qi < QT; ++qi) {
-                float d = 0.f;
+                float da = 0.f, db = 0.f;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) d = fmaf(q[qi][j], kf[j], d);
+                for (int j = 0; j < 16; j += 2) st_fma2(da, db, q[qi][j], q[qi][j + 1], kf[j], kf[j + 1]);
                 // this lane's group: scale_k * (q . code - zp_k * sum q) over its 16 values, already in log2 units
-                s[qi] = ksc[u] * (d - kzp[u] * qsum[qi]);
+                s[qi] = ksc[u] * ((da + db) - kzp[u] * qsum[qi]);
             }
 #pragma unroll
             for (int m = 1; m < LPK; m <<= 1)
@@ -178,19 +196,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_stream_kernel(AttnArgs a, int
             for (int qi = 0; qi < QT; ++qi) {
                 const float x = ok[u] ? s[qi] : -FLT_MAX;
                 if (x > m_run[qi] + 8.f) {           // lazy rescale: p stays below 2^8
-                    const float alpha = exp2f(m_run[qi] - x);
+                    const float alpha = st_ex2(m_run[qi] - x);
                     m_run[qi] = x;
                     l_run[qi] *= alpha;
                     corr[qi] *= alpha;
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[qi][j] *= alpha;
                 }
-                const float p = ok[u] ? exp2f(x - m_run[qi]) : 0.f;
+                const float p = ok[u] ? st_ex2(x - m_run[qi]) : 0.f;
                 l_run[qi] += p;
                 const float pv = p * vsc[u];
                 corr[qi] = fmaf(pv, vzp[u], corr[qi]);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[qi][j] = fmaf(pv, vf[j], acc[qi][j]);
+                for (int j = 0; j < 16; j += 2) st_fma2(acc[qi][j], acc[qi][j + 1], pv, pv, vf[j], vf[j + 1]);
             }
         }
     }
