@@ -17,6 +17,13 @@ struct AttnArgs {
     int splits, tiles_per_split;
     int n_qtiles;               // query tiles per (sample, head); grids are 1-D: ((b*H + h) * n_qtiles + qtile) * splits + split
     float* ws;                  // partials: [(b,h,qtile,split)][QT*(2+D)]
+    // Tensor-core kernel: per-tile parameter streams written by its preparation kernel, one block per (sample, head, key tile):
+    // softmax tables, normaliser records, then (when the packed-half converters apply) the (key, group) records of K and of V,
+    // each followed by a 16-byte trailer whose first word says that the tile needs the fp32 converter.
+    unsigned char* prep = nullptr;
+    long long prep_bh_stride = 0;
+    int prep_tile_stride = 0, prep_off_vn = 0, prep_off_krec = 0, prep_off_vrec = 0;
+    int prep_krec_bytes = 0, prep_vrec_bytes = 0;       // 0 = no records
 };
 
 __device__ __forceinline__ float load_q_elem(const void* q, int dtype, long long off) {
@@ -91,7 +98,8 @@ bool attn_stream_eligible(const AttnArgs& a, int kb, int vb);
 size_t attn_stream_workspace_bytes(int B, int H, int Lq, int Lk, int D);
 int attn_stream_run(AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
 bool attn_tc_eligible(const AttnArgs& a, int kb, int vb);
-int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st);
+int attn_tc_run(const AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
+size_t attn_tc_workspace_bytes(int B, int H, int Lk, int D);
 int attn_tc_status(int* out);
 
 }  // namespace varq

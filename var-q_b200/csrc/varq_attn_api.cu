@@ -17,7 +17,9 @@ extern "C" size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, in
     (void)k_store_bits; (void)v_store_bits;
     if (B <= 0 || H <= 0 || Lq <= 0 || Lk <= 0 || D <= 0) return 0;
     const size_t s1 = attn_small_workspace_bytes(B, H, Lq, Lk, D), s2 = attn_stream_workspace_bytes(B, H, Lq, Lk, D);
-    return s1 > s2 ? s1 : s2;
+    const size_t s3 = attn_tc_workspace_bytes(B, H, Lk, D);
+    const size_t s12 = s1 > s2 ? s1 : s2;
+    return s12 > s3 ? s12 : s3;
 }
 
 extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_codes, const varq_tensor_t* v_codes,
@@ -62,7 +64,7 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     const int force = __atomic_load_n(&g_forced_path, __ATOMIC_RELAXED);
     const bool small_q = Lq <= 4 || (Lq <= 16 && Lk <= 256);
     const bool want_tc = force ? (force == VARQ_ATTN_PATH_TC) : !small_q;
-    if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, (cudaStream_t)stream);
+    if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     const bool want_stream = force ? (force == VARQ_ATTN_PATH_STREAM) : small_q;
     if (want_stream && attn_stream_eligible(a, kb, vb)) return attn_stream_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     return attn_small_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);

@@ -27,8 +27,17 @@
 
 namespace varq {
 
-constexpr int TC_THREADS = 512;   // 8 softmax warps, 4 K-producer warps, 3 V-producer warps, 1 MMA warp
-constexpr int TC_VPROD = 96;      // V-producer threads
+// Warp roles of a CTA: 8 softmax warps, KW K-producer warps, VW V-producer warps, then the MMA warp.  The producers are
+// latency-bound (a warp retires an instruction every ~6 cycles), so the conversion of a tile is spread over many of them;
+// the folded-query mode keeps 4 + 3 because its K producers own one query row each.
+template <int KM> struct TcRoles {
+    static constexpr int KW = 4;
+    static constexpr int VW = 3;
+    static constexpr int KTHR = KW * 32, VTHR = VW * 32;
+    static constexpr int K_WARP0 = 8, V_WARP0 = 8 + KW, MMA_WARP = 8 + KW + VW;
+    static constexpr int LOAD_WARP = MMA_WARP + 1;        // issues the bulk copies (not in the folded-query mode)
+    static constexpr int THREADS = (MMA_WARP + (KM == 2 ? 1 : 2)) * 32;
+};
 constexpr int TC_M = 128;
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 20;
 
@@ -207,10 +216,14 @@ template <int D, int NQ, int KM> struct TcPlan {
     static constexpr int OFF_V = OFF_K + 2 * KT * KV_BYTES;   // [2]
     static constexpr int OFF_P = (OFF_V + 2 * V_BYTES + 1023) / 1024 * 1024;   // [PST]
     static constexpr int OFF_PK = OFF_P + PST * P_BYTES;      // [2][K, V]
-    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [4][3][N]: K scale, mask bias + log2(V scale), K zp * scale
-    static constexpr int OFF_BAR = OFF_KS + 4 * 3 * N * 4;    // mbarriers
-    static constexpr int N_BARS = 19;
-    static constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;     // tmem base, abort flag
+    // per-key softmax tables, a ring of TAB_SLOTS tiles: K scale, mask bias + log2(V scale), K zp * scale; with a dequantised K
+    // the first is a constant and the last is zero, so only the middle row is kept
+    static constexpr int TAB_ROWS = KS ? 1 : 3;
+    static constexpr int TAB_SLOTS = KM == KM_FOLD ? 4 : 8;
+    static constexpr int OFF_KS = OFF_PK + 4 * PK_BYTES;      // float [TAB_SLOTS][TAB_ROWS][N]
+    static constexpr int OFF_BAR = OFF_KS + TAB_SLOTS * TAB_ROWS * N * 4;    // mbarriers
+    static constexpr int N_BARS = 27;
+    static constexpr int OFF_MISC = OFF_BAR + (N_BARS + 1) / 2 * 16;     // tmem base, abort flag (everything below stays 16-byte aligned)
     static constexpr int OFF_PREF = OFF_MISC + 16;            // ParamRef [2]: K and V parameter records of the fp32 converters
     static constexpr int OFF_XCH = OFF_PREF + 2 * 48;         // float [2][128]: the two halves of a row exchange their reference maxima
     static constexpr int OFF_QSUM = OFF_XCH + 2 * 128 * 4;    // float [128]: row sums of Q (zero-point term of K)
@@ -220,7 +233,11 @@ template <int D, int NQ, int KM> struct TcPlan {
     static constexpr int OFF_VRAW = OFF_KRAW + TC_PAR_ENTRIES * 8;   // same for V
     static constexpr int OFF_ROWC = OFF_VRAW + TC_PAR_ENTRIES * 8;   // KM_FOLD: float [4][128] zero-point constants of the rows, per table slot; float [128] accumulation
     static constexpr int OFF_TILES = OFF_ROWC + (KM == KM_FOLD ? 5 * 128 * 4 : 0);   // KM_FOLD: int2 [TC_MAX_TILES] (first key, keys << 16 | row)
-    static constexpr int TOTAL = OFF_TILES + (KM == KM_FOLD ? TC_MAX_TILES * 8 : 0);
+    static constexpr int OFF_VNST = OFF_TILES + (KM == KM_FOLD ? TC_MAX_TILES * 8 : 0);   // uint2 [2][N]: staged normaliser records of a V tile
+    static constexpr int TOTAL = OFF_VNST + (KM == KM_FOLD ? 0 : 2 * N * 8);
+    // destinations of bulk copies
+    static_assert(OFF_PK % 16 == 0 && OFF_KS % 16 == 0 && OFF_KPAR % 16 == 0 && OFF_VPAR % 16 == 0 && OFF_KRAW % 16 == 0 &&
+                  OFF_VRAW % 16 == 0 && OFF_VNST % 16 == 0 && PK_BYTES % 16 == 0, "bulk copies need 16-byte aligned destinations");
     // TMEM columns: S double-buffered, then one accumulator per half of the keys:
     // D output columns followed by 16 columns of sum_k P * (small tile)
     static constexpr int ACC_COLS = D + 32;
@@ -434,16 +451,16 @@ __device__ __noinline__ void dequant_tile(unsigned char* tile, const uint32_t* p
 // group-wise) keep an essentially exact QK^T at the price of a second MMA.
 template <int BITS>
 __device__ __noinline__ void dequant_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed,
-                                                   int n_valid, int N, int W, int ptid, const ParamRef* pv_smem, int k0) {
+                                                   int n_valid, int N, int W, int ptid, const ParamRef* pv_smem, int k0, int nthr) {
     const ParamRef pv = *pv_smem;
     constexpr int VPW = 32 / BITS;
     const int total = N * W;
     const int wshift = __ffs(W) - 1;
     const bool uniform = (pv.group % VPW) == 0;
-    const bool fixed_w = (128 & (W - 1)) == 0;       // this thread's word column never changes
+    const bool fixed_w = (nthr & (W - 1)) == 0;       // this thread's word column never changes
     WordParams<VPW> wp;
     wp.row = -1;
-    for (int idx = ptid; idx < total; idx += 128) {
+    for (int idx = ptid; idx < total; idx += nthr) {
         const int key = idx >> wshift, w = idx & (W - 1);
         __half hh[VPW], hl[VPW];
         if (key < n_valid) {
@@ -494,7 +511,7 @@ template <int MAXE> struct ParStage {
             if (key < n_valid) {
                 const long long pi = base + pv.row(k0 + key) * pv.sr + (long long)g * pv.sg;
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + e)), "l"(pv.scale + pi) : "memory");
-                if (pv.zp) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + MAXE * nthr + e)), "l"(pv.zp + pi) : "memory");
+                if (pv.zp) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(raw + TC_PAR_ENTRIES + e)), "l"(pv.zp + pi) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -507,7 +524,7 @@ template <int MAXE> struct ParStage {
         for (int i = 0; i < MAXE; ++i) {
             const int e = ptid + i * nthr;
             if (e >= n_entries) continue;
-            const float sv = raw[e], zv = has_zp ? raw[MAXE * nthr + e] : 0.f;
+            const float sv = raw[e], zv = has_zp ? raw[TC_PAR_ENTRIES + e] : 0.f;
             const __half s_hi = __float2half_rn(sv);
             const __half s_lo = __float2half_rn(sv - __half2float(s_hi));
             const __half zb = __float2half_rn(1024.f + bias + zv);
@@ -522,11 +539,11 @@ template <int MAXE> struct ParStage {
 // K: hi + lo operand tiles from the staged records; each thread converts 16 bytes (4 words) of one key at a time.
 template <int BITS>
 __device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed, const uint2* par,
-                                              int n_valid, int N, int W, int ptid, int g_shift, int grp_shift) {
+                                              int n_valid, int N, int W, int ptid, int nthr, int g_shift, int grp_shift) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
     ItemWalk<false> wk;      // the items of a key share a parameter record: neighbouring lanes read it together
 #pragma unroll 1
-    for (wk.init(ptid, N, W >> 2, 128); wk.more(); wk.next()) {
+    for (wk.init(ptid, N, W >> 2, nthr); wk.more(); wk.next()) {
         const int key = wk.key, wi = wk.item << 2;
         uint32_t hi[4 * HW], lo[4 * HW];
         if (key < n_valid) {
@@ -669,12 +686,14 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 // raw scores -> x = s * ks + b2 [- kzs * qsum] in place (log2 domain, V scale folded in); returns their maximum
-template <bool KZ>
-__device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* ks, const float* b2, const float* kzs, float qsum) {
+// KC: the K scale is the same constant `kconst` for every key (a dequantised K carries its own scales)
+template <bool KZ, bool KC = false>
+__device__ __forceinline__ float chunk_scores(uint32_t (&rw)[32], const float* ks, const float* b2, const float* kzs, float qsum,
+                                              float kconst = 0.f) {
     float m0 = -FLT_MAX, m1 = -FLT_MAX;
 #pragma unroll
     for (int c = 0; c < 32; c += 4) {
-        const float4 s4 = tab4(ks, c), b4 = tab4(b2, c);
+        const float4 s4 = KC ? make_float4(kconst, kconst, kconst, kconst) : tab4(ks, c), b4 = tab4(b2, c);
         float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (KZ) z4 = tab4(kzs, c);
         float x[4];
@@ -706,18 +725,19 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&x)[32], float m, uint
 // becomes the reference of the rows that need one, and the accumulator (D output columns + 16 columns of
 // normaliser sums) is multiplied by 2^(old - new).  `pv_done` = barrier of the previous tile's O += P V
 // (nullptr at the first tile, whose MMA overwrites the accumulator).  Returns the row's reference, NaN if a wait expired.
-template <int D, int N>
+template <int D, int N, bool KC>
 __device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const float* ks, const float* b2, const float* kzs, bool k_zp,
                                             float qsum, float m_used, uint32_t acc, uint64_t* pv_done, uint32_t pv_parity,
-                                            volatile int* abort_flag) {
+                                            volatile int* abort_flag, float kconst) {
     uint32_t rw[32];
     float tm = -FLT_MAX;
 #pragma unroll 1
     for (int c = 0; c < nch; ++c) {
         tmem_ld32(s_addr + c * 32, rw);
         tmem_wait_ld();
-        tm = fmaxf(tm, k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
-                            : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum));
+        tm = fmaxf(tm, KC     ? chunk_scores<false, true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum, kconst)
+                       : k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
+                              : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum));
     }
     float alpha = 1.f;
     if (tm > m_used + TC_LAZY) {
@@ -747,9 +767,87 @@ __device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const floa
     return m_used;
 }
 
+// ---------------------------------------------------------------- preparation kernel
+// Everything the main kernel needs per key besides the packed codes, computed once per (sample, head) instead of once per
+// query tile: one thread block per key tile, one thread per key.  Block layout (byte offsets in AttnArgs):
+//   softmax tables  float [rows][N]   rows = 3 (K scale * softmax_scale * log2 e, mask bias + log2 of the folded V scale,
+//                                     K zero-point * that scale) or 1 (the middle row, when K is dequantised)
+//   normaliser      uint2 [N]         fp16 (hi, lo) of 2^-6 / V scale and of 2^-8 * V zero-point (1 and 0 when V is dequantised)
+//   K records       uint2 [N * groups] + 16-byte trailer     (only for the packed-half converter; see ParStage)
+//   V records       the same
+template <int N>
+__global__ void __launch_bounds__(N) tc_prepare_kernel(AttnArgs a, int n_tiles, int k_split, int k_ng, int v_ng, int kb, int vb) {
+    const int t = threadIdx.x;
+    const int j = (int)(blockIdx.x % (unsigned)n_tiles), bh = (int)(blockIdx.x / (unsigned)n_tiles), b = bh / a.H, h = bh - b * a.H;
+    const int key = j * N + t;
+    const bool valid = key < a.Lk;
+    unsigned char* blk = a.prep + (long long)bh * a.prep_bh_stride + (long long)j * a.prep_tile_stride;
+    const bool v_exact = a.vp.group == a.D;
+    const int krow = valid ? a.kp.row(key) : 0, vrow = valid ? a.vp.row(key) : 0;
+
+    float sc = 0.f, zs = 0.f, vsc = 1.f, vz = 0.f;
+    if (valid) {
+        if (!k_split) {
+            const long long pi = a.kp.index(b, krow, h, 0);
+            sc = __ldg(a.kp.scale + pi);
+            if (a.kp.zp) zs = __ldg(a.kp.zp + pi);
+        }
+        if (v_exact) {
+            const long long vi = a.vp.index(b, vrow, h, 0);
+            vsc = __ldg(a.vp.scale + vi);
+            if (a.vp.zp) vz = __ldg(a.vp.zp + vi);
+        }
+    }
+    float* tab = reinterpret_cast<float*>(blk);
+    const float b2 = (valid ? 0.f : -1e30f) + __log2f(fmaxf(vsc, TC_VS_MIN));
+    if (k_split) {
+        tab[t] = b2;
+    } else {
+        const float scl = sc * a.scale_log2;
+        tab[t] = scl;
+        tab[N + t] = b2;
+        tab[2 * N + t] = zs * scl;
+    }
+    {
+        const float vin = TC_AUX_DOWN * __frcp_rn(fmaxf(vsc, TC_VS_MIN)), vzd = vz * TC_ZP_DOWN;
+        const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
+        const __half vin_lo = __float2half_rn(vin - __half2float(vin_hi)), vz_lo = __float2half_rn(vzd - __half2float(vz_hi));
+        reinterpret_cast<uint2*>(blk + a.prep_off_vn)[t] =
+            make_uint2((uint32_t)__half_as_ushort(vin_hi) | ((uint32_t)__half_as_ushort(vin_lo) << 16),
+                       (uint32_t)__half_as_ushort(vz_hi) | ((uint32_t)__half_as_ushort(vz_lo) << 16));
+    }
+    // (key, group) records of the packed-half converters; a record outside their bounds flags the whole tile
+    auto records = [&](const ParamView& pv, int row, int ng, int bits, int off, int bytes) {
+        if (bytes == 0) return;         // block-uniform
+        uint2* rec = reinterpret_cast<uint2*>(blk + off) + t * ng;
+        const float bias = bits == 8 ? 128.f : bits == 4 ? 8.f : 2.f;
+        bool slow = false;
+        for (int g = 0; g < ng; ++g) {
+            uint2 r = make_uint2(0u, 0u);
+            if (valid) {
+                const long long pi = pv.index(b, row, h, g * pv.group);
+                const float sv = __ldg(pv.scale + pi), zv = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+                const __half s_hi = __float2half_rn(sv);
+                const __half s_lo = __float2half_rn(sv - __half2float(s_hi));
+                const __half zb = __float2half_rn(1024.f + bias + zv);
+                slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);     // code - zp stays below 2^10, the product inside fp16
+                r = make_uint2((uint32_t)__half_as_ushort(s_hi) | ((uint32_t)__half_as_ushort(s_lo) << 16),
+                               (uint32_t)__half_as_ushort(zb) * 0x10001u);
+            }
+            rec[g] = r;
+        }
+        const int any_slow = __syncthreads_or(slow ? 1 : 0);
+        if (t == 0) *reinterpret_cast<uint4*>(blk + off + N * ng * 8) = make_uint4((uint32_t)any_slow, 0u, 0u, 0u);
+    };
+    records(a.kp, krow, k_ng, kb, a.prep_off_krec, a.prep_krec_bytes);
+    records(a.vp, vrow, v_ng, vb, a.prep_off_vrec, a.prep_vrec_bytes);
+}
+
 template <int D, int NQ, int KM>
-__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int kb, int vb) {
+__global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnArgs a, int kb, int vb) {
     using P = TcPlan<D, NQ, KM>;
+    using R = TcRoles<KM>;
+    constexpr int KTHR = R::KTHR, VTHR = R::VTHR, MMA_WARP = R::MMA_WARP;
     constexpr int N = P::N;
     constexpr bool KS = KM == KM_SPLIT, QF = KM == KM_FOLD;
     static_assert(!QF || NQ == 2, "folded queries are fp16 hi + lo pairs");
@@ -763,8 +861,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     uint64_t* bar_p = bars + 8;       // [2] P written (the softmax threads that own real query rows)
     uint64_t* bar_pv = bars + 10;     // [2] O += P V complete (tcgen05.commit): V stage and P buffer free
     uint64_t* bar_o = bars + 12;      // all MMAs complete
-    uint64_t* bar_t = bars + 13;      // [4] per-key tables of tile j written (slot j % 4; 128 producers)
     uint64_t* bar_pkv = bars + 17;    // [2] packed V rows landed (tx bytes)
+    uint64_t* bar_t = bars + 19;      // [TAB_SLOTS] per-key tables of tile j in place (slot j % TAB_SLOTS): tx bytes, or the K producers (KM_FOLD)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
 
@@ -785,13 +883,50 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int32_t* vbase = a.vc + b * a.vs_b + h * a.vs_h;
     const int aq = (nq + 31) >> 5;                  // TMEM lane quarters that hold real queries
     float* s_qsum = reinterpret_cast<float*>(smem + P::OFF_QSUM);
+    // Everything a tile needs arrives by bulk copies on three barriers: the packed K rows (and, for the packed-half converter,
+    // the tile's (key, group) records) on bar_pk, the same for V plus the normaliser records on bar_pkv, the softmax tables
+    // on bar_t.  In the folded-query mode only the packed rows travel this way.
+    const unsigned char* prep_bh = a.prep + (long long)bh * a.prep_bh_stride;
+    auto issue_k = [&](int j) {
+        const int s = j & 1;
+        const uint32_t kbytes = (uint32_t)tile_n(j) * wk * 4;
+        if constexpr (QF) {
+            mbar_expect_tx(&bar_pk[s], kbytes);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)tile_k0(j) * wk, kbytes, &bar_pk[s]);
+        } else {
+            const unsigned char* blk = prep_bh + (long long)j * a.prep_tile_stride;
+            mbar_expect_tx(&bar_pk[s], kbytes + (uint32_t)a.prep_krec_bytes);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)tile_k0(j) * wk, kbytes, &bar_pk[s]);
+            if (a.prep_krec_bytes)
+                bulk_copy_g2s(smem + (s ? P::OFF_KRAW : P::OFF_KPAR), blk + a.prep_off_krec, (uint32_t)a.prep_krec_bytes, &bar_pk[s]);
+            constexpr uint32_t tab_bytes = P::TAB_ROWS * N * 4;
+            uint64_t* bt = &bar_t[j & (P::TAB_SLOTS - 1)];
+            mbar_expect_tx(bt, tab_bytes);
+            bulk_copy_g2s(smem + P::OFF_KS + (j & (P::TAB_SLOTS - 1)) * tab_bytes, blk, tab_bytes, bt);
+        }
+    };
+    auto issue_v = [&](int j) {
+        const int s = j & 1;
+        const uint32_t vbytes = (uint32_t)tile_n(j) * wv * 4;
+        if constexpr (QF) {
+            mbar_expect_tx(&bar_pkv[s], vbytes);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)tile_k0(j) * wv, vbytes, &bar_pkv[s]);
+        } else {
+            const unsigned char* blk = prep_bh + (long long)j * a.prep_tile_stride;
+            mbar_expect_tx(&bar_pkv[s], vbytes + (uint32_t)a.prep_vrec_bytes + N * 8);
+            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)tile_k0(j) * wv, vbytes, &bar_pkv[s]);
+            bulk_copy_g2s(smem + P::OFF_VNST + s * N * 8, blk + a.prep_off_vn, N * 8, &bar_pkv[s]);
+            if (a.prep_vrec_bytes)
+                bulk_copy_g2s(smem + (s ? P::OFF_VRAW : P::OFF_VPAR), blk + a.prep_off_vrec, (uint32_t)a.prep_vrec_bytes, &bar_pkv[s]);
+        }
+    };
 
     if (warp == 0) {
         // one lane per mbarrier: [0,2) packed K, [2,4) K tile, [4,6) V tile, [6,8) S, [8,10) P, [10,12) O += P V,
-        // 12 all MMAs, [13,17) tables, [17,19) packed V
+        // 12 all MMAs, [17,19) packed V, [19,27) tables
         if (lane < P::N_BARS) {
-            const uint32_t count = (lane >= 2 && lane < 4) || (lane >= 13 && lane < 17) ? 128u
-                                 : (lane >= 4 && lane < 6)   ? (uint32_t)TC_VPROD
+            const uint32_t count = (lane >= 2 && lane < 4) || (QF && lane >= 19) ? (uint32_t)KTHR
+                                 : (lane >= 4 && lane < 6)   ? (uint32_t)VTHR
                                  : (lane >= 8 && lane < 10)  ? (uint32_t)(64 * aq)     // only the warps that own real query rows take part
                                                              : 1u;
             mbar_init(&bars[lane], count);
@@ -827,18 +962,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         __syncwarp();
         if (lane == 0) {
             // the first two packed tiles are requested right away; their latency overlaps the rest of the set-up
-            for (int j = 0; j < 2 && j < t_first; ++j) {
-                const uint32_t rows = (uint32_t)tile_n(j);
-                const long long k0 = tile_k0(j);
-                mbar_expect_tx(&bar_pk[j], rows * wk * 4);
-                bulk_copy_g2s(smem + P::OFF_PK + (2 * j) * P::PK_BYTES, kbase + k0 * wk, rows * wk * 4, &bar_pk[j]);
-                mbar_expect_tx(&bar_pkv[j], rows * wv * 4);
-                bulk_copy_g2s(smem + P::OFF_PK + (2 * j + 1) * P::PK_BYTES, vbase + k0 * wv, rows * wv * 4, &bar_pkv[j]);
-            }
+            for (int j = 0; j < 2 && j < t_first; ++j) { issue_k(j); issue_v(j); }
         }
     }
     if (tid < 128) s_qsum[tid] = 0.f;
-    if (warp == 15) {   // TMEM allocation by one full warp
+    if (warp == MMA_WARP) {   // TMEM allocation by one full warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)P::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -849,7 +977,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
     const int T = QF ? sched[0] : (a.Lk + N - 1) / N;
     const int longest_tile = QF ? sched[1] : min(N, a.Lk);
 
-    if (!QF && (warp < 8 || warp == 15)) {
+    if (!QF && (warp < 8 || warp == MMA_WARP)) {
         // ---- Q tile -> shared (fp16 hi [, lo]) by the softmax and MMA warps; the producers are already at work
         constexpr int CH = D / 8;   // 16-byte chunks per row
         const int qtid = warp < 8 ? tid : 256 + lane;
@@ -910,13 +1038,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         for (int j = 0; j < T; ++j) {
             const int buf = j & 1;
             // per-key tables visible, S complete, and the P buffer free (the MMA that read it two tiles ago is done)
-            ok = ok && mbar_wait3(&bar_t[j & 3], (j >> 2) & 1, &bar_s[buf], (j >> 1) & 1,
+            ok = ok && mbar_wait3(&bar_t[j & (P::TAB_SLOTS - 1)], (j / P::TAB_SLOTS) & 1, &bar_s[buf], (j >> 1) & 1,
                                   &bar_pv[(j - P::PST) & 1], ((j - P::PST) >> 1) & 1, j >= P::PST, abort_flag, 11);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & 3) * 3 * N + half * NH;
-            const float* b2 = ks + N;
-            const float* kzs = ks + 2 * N;
+            const float* ks = reinterpret_cast<const float*>(smem + P::OFF_KS) + (j & (P::TAB_SLOTS - 1)) * P::TAB_ROWS * N + half * NH;
+            const float* b2 = KS ? ks : ks + N;                 // a dequantised K keeps the middle row only
+            const float* kzs = KS ? ks : ks + 2 * N;
             const uint32_t s_addr = lane_base + P::COL_S + buf * N + half * NH;
             // 32-key chunks of this half that hold at least one key
             const int nch = min(NH / 32, max(0, (tile_n(j) - half * NH + 31) >> 5));
@@ -930,15 +1058,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
                     uint32_t rw[32];
                     tmem_ld32(s_addr + c * 32, rw);
                     tmem_wait_ld();
-                    const float cm = k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
-                                          : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum);
+                    const float cm = KS     ? chunk_scores<false, true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum, a.scale_log2)
+                                     : k_zp ? chunk_scores<true>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum)
+                                            : chunk_scores<false>(rw, ks + c * 32, b2 + c * 32, kzs + c * 32, qsum);
                     if (m_used == -FLT_MAX) m_used = cm;    // first chunk this thread ever sees: its maximum is the reference
                     if (__any_sync(0xffffffffu, cm > m_used + TC_LAZY)) {
                         // Rare: some row of this warp meets a score more than 2^12 above its reference.  A new
                         // reference is taken, the accumulator rescaled, and the tile's chunks are redone
                         // (P of earlier chunks was written against the old reference).
-                        m_used = new_reference<D, N>(s_addr, nch, ks, b2, kzs, k_zp, qsum, m_used, acc,
-                                                     j > 0 ? &bar_pv[(j - 1) & 1] : nullptr, ((j - 1) >> 1) & 1, abort_flag);
+                        m_used = new_reference<D, N, KS>(s_addr, nch, ks, b2, kzs, k_zp, qsum, m_used, acc,
+                                                         j > 0 ? &bar_pv[(j - 1) & 1] : nullptr, ((j - 1) >> 1) & 1, abort_flag, a.scale_log2);
                         ok = __all_sync(0xffffffffu, m_used == m_used);
                         if (!ok) break;
                         c = 0;
@@ -1005,333 +1134,429 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
             }
         }
         tc_fence_before();
-    } else if (warp < 12) {
-        // =============================================================== K producers (and per-key tables)
-        const int ptid = tid - 256;
-        auto issue = [&](int j) {
-            const int s = j & 1;
-            const uint32_t kbytes = (uint32_t)tile_n(j) * wk * 4;
-            mbar_expect_tx(&bar_pk[s], kbytes);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)tile_k0(j) * wk, kbytes, &bar_pk[s]);
-        };
-        bool ok = true;
-        int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
-        const bool v_exact = a.vp.group == D;
-        // per-key parameters of a tile are fetched one tile ahead so the global-load latency is hidden
-        float nsc = 0.f, nzs = 0.f, nvsc = 1.f;
-        const long long k_par = a.kp.index(b, 0, h, 0), v_par = a.vp.index(b, 0, h, 0);   // (sample, head) part of the parameter index
-        auto fetch_params = [&](int j) {
-            nsc = 0.f; nzs = 0.f; nvsc = 1.f;
-            if (j < T && ptid < tile_n(j)) {
-                const int key = tile_k0(j) + ptid;
-                if constexpr (KM != KM_EXACT) {
-                    nsc = 1.f;                       // S needs only softmax_scale * log2(e)
-                } else {
-                    const long long pi = k_par + a.kp.row(key) * a.kp.sr;
-                    nsc = __ldg(a.kp.scale + pi);
-                    if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
-                }
-                if (v_exact) nvsc = __ldg(a.vp.scale + v_par + a.vp.row(key) * a.vp.sr);
-            }
-        };
-        fetch_params(0);
-        // KM_SPLIT: (key, group) records of the tile, staged one tile ahead, for the packed-half converter
-        const int k_vpw = 32 / kb;
-        const int k_ng = D / a.kp.group;                                   // groups per key
-        const bool k_fast = KS && (a.kp.group % k_vpw) == 0 && (a.kp.group & (a.kp.group - 1)) == 0 && N * k_ng <= 2 * 128 && N * k_ng <= TC_PAR_ENTRIES;
-        const int k_gshift = __ffs(k_ng) - 1, k_grp_shift = __ffs(a.kp.group) - 1;
-        uint2* kpar = reinterpret_cast<uint2*>(smem + P::OFF_KPAR);
-        const ParamRef* k_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF);
-        if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF) = param_ref(a.kp, b, h);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        using KStage = ParStage<2>;            // two records per thread: groups of 32 or more at either head_dim
-        float* kraw = reinterpret_cast<float*>(smem + P::OFF_KRAW);
-        if (k_fast) KStage::request(a.kp, k_par, tile_k0(0), tile_n(0), k_gshift, ptid, 128, kraw);
-        // KM_FOLD: the row (appended step) whose scales the Q operand currently carries, and this thread's row constant
-        int q_row = -1;
-        float my_rowc = 0.f;
-        for (int j = 0; j < T; ++j) {
-            const int s = j & 1;
-            const int n_valid = tile_n(j);
-            const int k0 = tile_k0(j);
-            const float sc = nsc, zs = nzs, vsc = nvsc;
-            const float bias = (ptid < n_valid) ? 0.f : -1e30f;
-            fetch_params(j + 1);
-            bool slow = !k_fast;
-            if (KS && k_fast) {
-                slow = KStage::build(kpar, kraw, n_valid << k_gshift, kb == 8 ? 128.f : kb == 4 ? 8.f : 2.f, a.kp.zp != nullptr, ptid, 128);
-                if (j + 1 < T) KStage::request(a.kp, k_par, tile_k0(j + 1), tile_n(j + 1), k_gshift, ptid, 128, kraw);   // consumed one tile later
-            }
-            ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
-            if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
-            if constexpr (KS) {
-                if (k_fast) {   // records visible to all producers; one record out of bounds sends the whole tile to the fp32 routine
-                    uint32_t any_slow;
-                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                                 : "=r"(any_slow) : "r"((uint32_t)slow) : "memory");
-                    slow = any_slow != 0;
-                }
-            }
-            if constexpr (QF) {
-                const int row = tile_row(j);
-                if (row != q_row) {
-                    // The tile starts a new step: Q * s(step) replaces the Q operand once S of the previous tile, the last
-                    // reader of the old one, is complete.  c = sum_d q_d s_d z_d of every query row goes to the row constants.
-                    // A thread keeps one 16-byte chunk column; its query chunks are requested eight at a time, ahead of the wait.
-                    constexpr int CH = D / 8;                       // 16-byte chunks per row
-                    constexpr int RSTEP = 128 / CH;                 // rows between two chunks of a thread
-                    constexpr int BATCH = 8;
-                    const int c = ptid % CH, r_first = ptid / CH;
-                    float sv[8], szv[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const long long pi = a.kp.index(b, row, h, c * 8 + e);
-                        sv[e] = __ldg(a.kp.scale + pi);
-                        szv[e] = a.kp.zp ? sv[e] * __ldg(a.kp.zp + pi) : 0.f;
-                    }
-                    float* racc = reinterpret_cast<float*>(smem + P::OFF_ROWC) + 4 * 128;
-                    float v[BATCH][8];
-                    auto load_batch = [&](int it0) {
-#pragma unroll
-                        for (int u = 0; u < BATCH; ++u) {
-                            const int r = r_first + (it0 + u) * RSTEP;
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
-                            if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v[u]);
-                        }
-                    };
-                    load_batch(0);
-                    if (j >= 1) ok = ok && mbar_wait(&bar_s[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 25);
-#pragma unroll 1
-                    for (int it0 = 0; it0 < TC_M / RSTEP; it0 += BATCH) {
-                        if (it0 > 0) load_batch(it0);
-#pragma unroll
-                        for (int u = 0; u < BATCH; ++u) {
-                            const int r = r_first + (it0 + u) * RSTEP;
-                            uint32_t hi[4], lo[4];
-                            float p0 = 0.f, p1 = 0.f;
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {      // packed fp32 pairs: two elements per instruction
-                                float x0, x1;
-                                fma2(p0, p1, v[u][2 * e], v[u][2 * e + 1], szv[2 * e], szv[2 * e + 1], p0, p1);
-                                fma2(x0, x1, v[u][2 * e], v[u][2 * e + 1], sv[2 * e], sv[2 * e + 1], 0.f, 0.f);
-                                x0 = fminf(fmaxf(x0, -65504.f), 65504.f);      // saturate instead of overflowing fp16
-                                x1 = fminf(fmaxf(x1, -65504.f), 65504.f);
-                                const __half2 hh = __floats2half2_rn(x0, x1);
-                                const float2 hf = __half22float2(hh);
-                                float y0, y1;
-                                add2(y0, y1, x0, x1, -hf.x, -hf.y);
-                                const __half2 ll = __floats2half2_rn(y0, y1);
-                                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                                lo[e] = *reinterpret_cast<const uint32_t*>(&ll);
-                            }
-                            float part = p0 + p1;
-                            const uint32_t off = tile_off(r, c * 8, TC_M);
-                            sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
-                            sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
-                            // the CH threads of a row are neighbouring lanes: fold their parts, one of them writes the row's constant
-#pragma unroll
-                            for (int m = 1; m < CH; m <<= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
-                            if (c == 0) racc[r] = part;
-                        }
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    my_rowc = racc[ptid] * a.scale_log2;
-                    q_row = row;
-                }
-                reinterpret_cast<float*>(smem + P::OFF_ROWC)[(j & 3) * 128 + ptid] = my_rowc;
-            }
-            const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
-            unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
-            if (ok) {
-                if constexpr (KS) {
-                    if (!slow) {
-                        if (kb == 8) group_split_tile<8>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
-                        else if (kb == 4) group_split_tile<4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
-                        else group_split_tile<2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, k_gshift, k_grp_shift);
+    } else if (warp < R::V_WARP0) {
+        if constexpr (QF) {
+            // =============================================================== K producers (and per-key tables)
+            const int ptid = tid - 256;
+            auto issue = [&](int j) {
+                const int s = j & 1;
+                const uint32_t kbytes = (uint32_t)tile_n(j) * wk * 4;
+                mbar_expect_tx(&bar_pk[s], kbytes);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * s) * P::PK_BYTES, kbase + (long long)tile_k0(j) * wk, kbytes, &bar_pk[s]);
+            };
+            bool ok = true;
+            int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
+            const bool v_exact = a.vp.group == D;
+            // per-key parameters of a tile are fetched one tile ahead so the global-load latency is hidden
+            float nsc = 0.f, nzs = 0.f, nvsc = 1.f;
+            const long long k_par = a.kp.index(b, 0, h, 0), v_par = a.vp.index(b, 0, h, 0);   // (sample, head) part of the parameter index
+            auto fetch_params = [&](int j) {
+                nsc = 0.f; nzs = 0.f; nvsc = 1.f;
+                if (j < T && ptid < tile_n(j)) {
+                    const int key = tile_k0(j) + ptid;
+                    if constexpr (KM != KM_EXACT) {
+                        nsc = 1.f;                       // S needs only softmax_scale * log2(e)
                     } else {
-                        if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
-                        else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
-                        else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0);
+                        const long long pi = k_par + a.kp.row(key) * a.kp.sr;
+                        nsc = __ldg(a.kp.scale + pi);
+                        if (a.kp.zp) nzs = __ldg(a.kp.zp + pi);
+                    }
+                    if (v_exact) nvsc = __ldg(a.vp.scale + v_par + a.vp.row(key) * a.vp.sr);
+                }
+            };
+            fetch_params(0);
+            // KM_SPLIT: (key, group) records of the tile, staged one tile ahead, for the packed-half converter
+            const int k_vpw = 32 / kb;
+            const int k_ng = D / a.kp.group;                                   // groups per key
+            const bool k_fast = KS && (a.kp.group % k_vpw) == 0 && (a.kp.group & (a.kp.group - 1)) == 0 && N * k_ng <= 2 * KTHR && N * k_ng <= TC_PAR_ENTRIES;
+            const int k_gshift = __ffs(k_ng) - 1, k_grp_shift = __ffs(a.kp.group) - 1;
+            uint2* kpar = reinterpret_cast<uint2*>(smem + P::OFF_KPAR);
+            const ParamRef* k_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF);
+            if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF) = param_ref(a.kp, b, h);
+            asm volatile("bar.sync 1, %0;" ::"n"(KTHR) : "memory");
+            using KStage = ParStage<2>;            // two records per thread: groups of 32 or more at either head_dim
+            float* kraw = reinterpret_cast<float*>(smem + P::OFF_KRAW);
+            if (k_fast) KStage::request(a.kp, k_par, tile_k0(0), tile_n(0), k_gshift, ptid, KTHR, kraw);
+            // KM_FOLD: the row (appended step) whose scales the Q operand currently carries, and this thread's row constant
+            int q_row = -1;
+            float my_rowc = 0.f;
+            for (int j = 0; j < T; ++j) {
+                const int s = j & 1;
+                const int n_valid = tile_n(j);
+                const int k0 = tile_k0(j);
+                const float sc = nsc, zs = nzs, vsc = nvsc;
+                const float bias = (ptid < n_valid) ? 0.f : -1e30f;
+                fetch_params(j + 1);
+                bool slow = !k_fast;
+                if (KS && k_fast) {
+                    slow = KStage::build(kpar, kraw, n_valid << k_gshift, kb == 8 ? 128.f : kb == 4 ? 8.f : 2.f, a.kp.zp != nullptr, ptid, KTHR);
+                    if (j + 1 < T) KStage::request(a.kp, k_par, tile_k0(j + 1), tile_n(j + 1), k_gshift, ptid, KTHR, kraw);   // consumed one tile later
+                }
+                ok = ok && mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
+                if (j >= 2) ok = ok && mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
+                if constexpr (KS) {
+                    if (k_fast) {   // records visible to all producers; one record out of bounds sends the whole tile to the fp32 routine
+                        uint32_t any_slow;
+                        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                     : "=r"(any_slow) : "r"((uint32_t)slow), "n"(KTHR) : "memory");
+                        slow = any_slow != 0;
+                    }
+                }
+                if constexpr (QF) {
+                    const int row = tile_row(j);
+                    if (row != q_row) {
+                        // The tile starts a new step: Q * s(step) replaces the Q operand once S of the previous tile, the last
+                        // reader of the old one, is complete.  c = sum_d q_d s_d z_d of every query row goes to the row constants.
+                        // A thread keeps one 16-byte chunk column; its query chunks are requested eight at a time, ahead of the wait.
+                        constexpr int CH = D / 8;                       // 16-byte chunks per row
+                        constexpr int RSTEP = 128 / CH;                 // rows between two chunks of a thread
+                        constexpr int BATCH = 8;
+                        const int c = ptid % CH, r_first = ptid / CH;
+                        float sv[8], szv[8];
+    #pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const long long pi = a.kp.index(b, row, h, c * 8 + e);
+                            sv[e] = __ldg(a.kp.scale + pi);
+                            szv[e] = a.kp.zp ? sv[e] * __ldg(a.kp.zp + pi) : 0.f;
+                        }
+                        float* racc = reinterpret_cast<float*>(smem + P::OFF_ROWC) + 4 * 128;
+                        float v[BATCH][8];
+                        auto load_batch = [&](int it0) {
+    #pragma unroll
+                            for (int u = 0; u < BATCH; ++u) {
+                                const int r = r_first + (it0 + u) * RSTEP;
+    #pragma unroll
+                                for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
+                                if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v[u]);
+                            }
+                        };
+                        load_batch(0);
+                        if (j >= 1) ok = ok && mbar_wait(&bar_s[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, 25);
+    #pragma unroll 1
+                        for (int it0 = 0; it0 < TC_M / RSTEP; it0 += BATCH) {
+                            if (it0 > 0) load_batch(it0);
+    #pragma unroll
+                            for (int u = 0; u < BATCH; ++u) {
+                                const int r = r_first + (it0 + u) * RSTEP;
+                                uint32_t hi[4], lo[4];
+                                float p0 = 0.f, p1 = 0.f;
+    #pragma unroll
+                                for (int e = 0; e < 4; ++e) {      // packed fp32 pairs: two elements per instruction
+                                    float x0, x1;
+                                    fma2(p0, p1, v[u][2 * e], v[u][2 * e + 1], szv[2 * e], szv[2 * e + 1], p0, p1);
+                                    fma2(x0, x1, v[u][2 * e], v[u][2 * e + 1], sv[2 * e], sv[2 * e + 1], 0.f, 0.f);
+                                    x0 = fminf(fmaxf(x0, -65504.f), 65504.f);      // saturate instead of overflowing fp16
+                                    x1 = fminf(fmaxf(x1, -65504.f), 65504.f);
+                                    const __half2 hh = __floats2half2_rn(x0, x1);
+                                    const float2 hf = __half22float2(hh);
+                                    float y0, y1;
+                                    add2(y0, y1, x0, x1, -hf.x, -hf.y);
+                                    const __half2 ll = __floats2half2_rn(y0, y1);
+                                    hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                                    lo[e] = *reinterpret_cast<const uint32_t*>(&ll);
+                                }
+                                float part = p0 + p1;
+                                const uint32_t off = tile_off(r, c * 8, TC_M);
+                                sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
+                                sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
+                                // the CH threads of a row are neighbouring lanes: fold their parts, one of them writes the row's constant
+    #pragma unroll
+                                for (int m = 1; m < CH; m <<= 1) part += __shfl_xor_sync(0xffffffffu, part, m);
+                                if (c == 0) racc[r] = part;
+                            }
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        my_rowc = racc[ptid] * a.scale_log2;
+                        q_row = row;
+                    }
+                    reinterpret_cast<float*>(smem + P::OFF_ROWC)[(j & 3) * 128 + ptid] = my_rowc;
+                }
+                const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
+                unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
+                if (ok) {
+                    if constexpr (KS) {
+                        if (!slow) {
+                            if (kb == 8) group_split_tile<8>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                            else if (kb == 4) group_split_tile<4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                            else group_split_tile<2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                        } else {
+                            if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
+                            else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
+                            else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
+                        }
+                    } else {
+                        const int krows = min(N, ((n_valid + N / 2 - 1) / (N / 2)) * (N / 2));   // softmax reads whole halves of a tile
+                        if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                        else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                        else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    }
+                    if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
+                        float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 3 * N;
+                        const float scl = sc * a.scale_log2;
+                        const float vsf = fmaxf(vsc, TC_VS_MIN);
+                        tab[ptid] = scl;
+                        tab[N + ptid] = bias + __log2f(vsf);
+                        tab[2 * N + ptid] = QF ? 1.f : zs * scl;      // KM_FOLD: the row constant is subtracted as it is
+                    }
+                    fence_async_smem();
+                    mbar_arrive(&bar_k[s]);
+                    mbar_arrive(&bar_t[j & 3]);
+                }
+
+                {   // every K producer is done with the packed stage; all 128 take the same decision on `ok`
+                    uint32_t all_ok;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(all_ok) : "r"((uint32_t)ok), "n"(KTHR) : "memory");
+                    ok = all_ok != 0;
+                }
+                if (!ok) break;
+                if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
+            }
+            if (!ok && ptid == 0) {
+                // drain: bulk copies already issued must land before the CTA may exit
+                for (int j = 0; j < issued; ++j) {
+                    bool landed = false;
+                    for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pk[j & 1], (j >> 1) & 1);
+                }
+            }
+        } else {
+            // =============================================================== K converters
+            // A tile's packed rows and parameter records arrive by bulk copy; the converters only wait, convert and arrive.
+            const int ptid = tid - 256;
+            const int k_ng = D / a.kp.group;                                   // groups per key
+            const bool k_fast = KS && a.prep_krec_bytes > 0;                 // records for the packed-half converter were prepared
+            const int k_gshift = __ffs(k_ng) - 1, k_grp_shift = __ffs(a.kp.group) - 1;
+            const ParamRef* k_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF);
+            if constexpr (KS) {
+                if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF) = param_ref(a.kp, b, h);
+                asm volatile("bar.sync 1, %0;" ::"n"(KTHR) : "memory");
+            }
+            for (int j = 0; j < T; ++j) {
+                const int s = j & 1;
+                const int n_valid = tile_n(j);
+                bool ok = mbar_wait(&bar_pk[s], (j >> 1) & 1, abort_flag, 21);
+                if (ok && j >= 2) ok = mbar_wait(&bar_s[s], ((j - 2) >> 1) & 1, abort_flag, 22);    // K stage is free
+                if (!ok) break;
+                const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
+                unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
+                if constexpr (KS) {
+                    const uint2* kpar = reinterpret_cast<const uint2*>(smem + (s ? P::OFF_KRAW : P::OFF_KPAR));
+                    // the trailer of the record block says whether a record of the tile is outside the packed-half converter's bounds
+                    const bool slow = !k_fast || reinterpret_cast<const uint32_t*>(kpar + (N << k_gshift))[0] != 0u;
+                    if (!slow) {
+                        if (kb == 8) group_split_tile<8>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                        else if (kb == 4) group_split_tile<4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                        else group_split_tile<2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                    } else {
+                        const int k0 = tile_k0(j);
+                        if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
+                        else if (kb == 4) dequant_split_tile<4>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
+                        else dequant_split_tile<2>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
                     }
                 } else {
                     const int krows = min(N, ((n_valid + N / 2 - 1) / (N / 2)) * (N / 2));   // softmax reads whole halves of a tile
-                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, 128, krows);
-                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, 128, krows);
-                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, 128, krows);
-                }
-                if (ptid < N) {   // table slot j % 4; the K scale carries softmax_scale * log2(e)
-                    float* tab = reinterpret_cast<float*>(smem + P::OFF_KS) + (j & 3) * 3 * N;
-                    const float scl = sc * a.scale_log2;
-                    const float vsf = fmaxf(vsc, TC_VS_MIN);
-                    tab[ptid] = scl;
-                    tab[N + ptid] = bias + __log2f(vsf);
-                    tab[2 * N + ptid] = QF ? 1.f : zs * scl;      // KM_FOLD: the row constant is subtracted as it is
+                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_k[s]);
-                mbar_arrive(&bar_t[j & 3]);
-            }
-
-            {   // every K producer is done with the packed stage; all 128 take the same decision on `ok`
-                uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
-                ok = all_ok != 0;
-            }
-            if (!ok) break;
-            if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
-        }
-        if (!ok && ptid == 0) {
-            // drain: bulk copies already issued must land before the CTA may exit
-            for (int j = 0; j < issued; ++j) {
-                bool landed = false;
-                for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pk[j & 1], (j >> 1) & 1);
             }
         }
-    } else if (warp < 15) {
-        // =============================================================== V producers
-        const int ptid = tid - 384;
-        auto issue = [&](int j) {
-            const int s = j & 1;
-            const uint32_t vbytes = (uint32_t)tile_n(j) * wv * 4;
-            mbar_expect_tx(&bar_pkv[s], vbytes);
-            bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)tile_k0(j) * wv, vbytes, &bar_pkv[s]);
-        };
-        bool ok = true;
-        int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
-        const bool v_exact = a.vp.group == D;
-        // The small operand tile of a stage (16 x N fp16, K-major): row 0/1 = hi/lo of 2^-6 / V scale, row 2/3 =
-        // hi/lo of 2^-8 * V zero-point of each key; rows 4-15 stay zero for the whole kernel.  Each thread looks
-        // after keys ptid and ptid + 96 and fetches their parameters one tile ahead.
-        constexpr int KPT = (N + TC_VPROD - 1) / TC_VPROD;
-        float nvs[KPT], nvz[KPT];
-        const long long v_par = a.vp.index(b, 0, h, 0);     // (sample, head) part of the parameter index
-        auto fetch_v = [&](int j) {
-#pragma unroll
-            for (int i = 0; i < KPT; ++i) {
-                nvs[i] = 1.f; nvz[i] = 0.f;
-                const int kt = ptid + i * TC_VPROD;
-                if (v_exact && j < T && kt < tile_n(j)) {
-                    const long long vi = v_par + a.vp.row(tile_k0(j) + kt) * a.vp.sr;
-                    nvs[i] = __ldg(a.vp.scale + vi);
-                    if (a.vp.zp) nvz[i] = __ldg(a.vp.zp + vi);
-                }
-            }
-        };
-        fetch_v(0);
-        // A V scale that varies along head_dim: (key, group) records staged one tile ahead for the packed-half converter,
-        // or, with per-element parameters that a step's tokens share (KM_FOLD tiles lie inside one step), a per-dim table
-        const int v_vpw = 32 / vb;
-        const int v_ng = D / a.vp.group;
-        const bool v_grouped = !v_exact && (a.vp.group % v_vpw) == 0 && (a.vp.group & (a.vp.group - 1)) == 0 && N * v_ng <= 3 * TC_VPROD;
-        const bool v_perdim = QF && !v_exact && !v_grouped && a.vp.row_of_token != nullptr && (D % (4 * v_vpw)) == 0;
-        const int v_gshift = __ffs(v_ng) - 1, v_grp_shift = __ffs(a.vp.group) - 1;
-        uint2* vpar = reinterpret_cast<uint2*>(smem + P::OFF_VPAR);
-        __half* vdim_s = reinterpret_cast<__half*>(smem + P::OFF_VPAR);
-        __half* vdim_sl = vdim_s + D;
-        __half* vdim_zb = vdim_s + 2 * D;
-        const float v_bias = vb == 8 ? 128.f : vb == 4 ? 8.f : 2.f;
-        int vdim_row = -1;
-        const ParamRef* v_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF + 48);
-        if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF + 48) = param_ref(a.vp, b, h);
-        using VStage = ParStage<3>;
-        float* vraw = reinterpret_cast<float*>(smem + P::OFF_VRAW);
-        if (v_grouped) VStage::request(a.vp, v_par, tile_k0(0), tile_n(0), v_gshift, ptid, TC_VPROD, vraw);
-        asm volatile("bar.sync 2, 96;" ::: "memory");
-        for (int j = 0; j < T; ++j) {
-            const int s = j & 1;
-            const int k0 = tile_k0(j);
-            const int n_valid = tile_n(j);
-            float vs[KPT], vz[KPT];
-#pragma unroll
-            for (int i = 0; i < KPT; ++i) { vs[i] = nvs[i]; vz[i] = nvz[i]; }
-            fetch_v(j + 1);
-            bool slow = !v_grouped && !v_perdim;
-            if (v_grouped) {
-                slow = VStage::build(vpar, vraw, n_valid << v_gshift, v_bias, a.vp.zp != nullptr, ptid, TC_VPROD);
-                if (j + 1 < T) VStage::request(a.vp, v_par, tile_k0(j + 1), tile_n(j + 1), v_gshift, ptid, TC_VPROD, vraw);   // consumed one tile later
-            } else if (v_perdim) {
-                const int row = a.vp.row(k0);
-                slow = a.vp.row(k0 + n_valid - 1) != row;            // the tile must lie inside one row of V's parameters
-                if (!slow && row != vdim_row) {
-                    for (int d = ptid; d < D; d += TC_VPROD) {
-                        const long long pi = a.vp.index(b, row, h, d);
-                        const float sv = __ldg(a.vp.scale + pi), zv = a.vp.zp ? __ldg(a.vp.zp + pi) : 0.f;
-                        const __half s_hi = __float2half_rn(sv);
-                        vdim_s[d] = s_hi;
-                        vdim_sl[d] = __float2half_rn(sv - __half2float(s_hi));
-                        vdim_zb[d] = __float2half_rn(1024.f + v_bias + zv);
-                        slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);
+    } else if (warp < MMA_WARP) {
+        if constexpr (QF) {
+            // =============================================================== V producers
+            const int ptid = tid - R::V_WARP0 * 32;
+            auto issue = [&](int j) {
+                const int s = j & 1;
+                const uint32_t vbytes = (uint32_t)tile_n(j) * wv * 4;
+                mbar_expect_tx(&bar_pkv[s], vbytes);
+                bulk_copy_g2s(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES, vbase + (long long)tile_k0(j) * wv, vbytes, &bar_pkv[s]);
+            };
+            bool ok = true;
+            int issued = min(T, 2);                    // tiles 0 and 1 were requested during set-up
+            const bool v_exact = a.vp.group == D;
+            // The small operand tile of a stage (16 x N fp16, K-major): row 0/1 = hi/lo of 2^-6 / V scale, row 2/3 =
+            // hi/lo of 2^-8 * V zero-point of each key; rows 4-15 stay zero for the whole kernel.  Each thread looks
+            // after keys ptid and ptid + 96 and fetches their parameters one tile ahead.
+            constexpr int KPT = (N + VTHR - 1) / VTHR;
+            float nvs[KPT], nvz[KPT];
+            const long long v_par = a.vp.index(b, 0, h, 0);     // (sample, head) part of the parameter index
+            auto fetch_v = [&](int j) {
+    #pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    nvs[i] = 1.f; nvz[i] = 0.f;
+                    const int kt = ptid + i * VTHR;
+                    if (v_exact && j < T && kt < tile_n(j)) {
+                        const long long vi = v_par + a.vp.row(tile_k0(j) + kt) * a.vp.sr;
+                        nvs[i] = __ldg(a.vp.scale + vi);
+                        if (a.vp.zp) nvz[i] = __ldg(a.vp.zp + vi);
                     }
                 }
-                vdim_row = slow ? -1 : row;
+            };
+            fetch_v(0);
+            // A V scale that varies along head_dim: (key, group) records staged one tile ahead for the packed-half converter,
+            // or, with per-element parameters that a step's tokens share (KM_FOLD tiles lie inside one step), a per-dim table
+            const int v_vpw = 32 / vb;
+            const int v_ng = D / a.vp.group;
+            const bool v_grouped = !v_exact && (a.vp.group % v_vpw) == 0 && (a.vp.group & (a.vp.group - 1)) == 0 && N * v_ng <= 3 * VTHR && N * v_ng <= TC_PAR_ENTRIES;
+            const bool v_perdim = QF && !v_exact && !v_grouped && a.vp.row_of_token != nullptr && (D % (4 * v_vpw)) == 0;
+            const int v_gshift = __ffs(v_ng) - 1, v_grp_shift = __ffs(a.vp.group) - 1;
+            uint2* vpar = reinterpret_cast<uint2*>(smem + P::OFF_VPAR);
+            __half* vdim_s = reinterpret_cast<__half*>(smem + P::OFF_VPAR);
+            __half* vdim_sl = vdim_s + D;
+            __half* vdim_zb = vdim_s + 2 * D;
+            const float v_bias = vb == 8 ? 128.f : vb == 4 ? 8.f : 2.f;
+            int vdim_row = -1;
+            const ParamRef* v_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF + 48);
+            if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF + 48) = param_ref(a.vp, b, h);
+            using VStage = ParStage<3>;
+            float* vraw = reinterpret_cast<float*>(smem + P::OFF_VRAW);
+            if (v_grouped) VStage::request(a.vp, v_par, tile_k0(0), tile_n(0), v_gshift, ptid, VTHR, vraw);
+            asm volatile("bar.sync 2, %0;" ::"n"(VTHR) : "memory");
+            for (int j = 0; j < T; ++j) {
+                const int s = j & 1;
+                const int k0 = tile_k0(j);
+                const int n_valid = tile_n(j);
+                float vs[KPT], vz[KPT];
+    #pragma unroll
+                for (int i = 0; i < KPT; ++i) { vs[i] = nvs[i]; vz[i] = nvz[i]; }
+                fetch_v(j + 1);
+                bool slow = !v_grouped && !v_perdim;
+                if (v_grouped) {
+                    slow = VStage::build(vpar, vraw, n_valid << v_gshift, v_bias, a.vp.zp != nullptr, ptid, VTHR);
+                    if (j + 1 < T) VStage::request(a.vp, v_par, tile_k0(j + 1), tile_n(j + 1), v_gshift, ptid, VTHR, vraw);   // consumed one tile later
+                } else if (v_perdim) {
+                    const int row = a.vp.row(k0);
+                    slow = a.vp.row(k0 + n_valid - 1) != row;            // the tile must lie inside one row of V's parameters
+                    if (!slow && row != vdim_row) {
+                        for (int d = ptid; d < D; d += VTHR) {
+                            const long long pi = a.vp.index(b, row, h, d);
+                            const float sv = __ldg(a.vp.scale + pi), zv = a.vp.zp ? __ldg(a.vp.zp + pi) : 0.f;
+                            const __half s_hi = __float2half_rn(sv);
+                            vdim_s[d] = s_hi;
+                            vdim_sl[d] = __float2half_rn(sv - __half2float(s_hi));
+                            vdim_zb[d] = __float2half_rn(1024.f + v_bias + zv);
+                            slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);
+                        }
+                    }
+                    vdim_row = slow ? -1 : row;
+                }
+                ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
+                if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
+                if (v_grouped || v_perdim) {   // tables visible to all producers; they agree on the converter
+                    uint32_t any_slow;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 2, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(any_slow) : "r"((uint32_t)slow), "n"(VTHR) : "memory");
+                    slow = any_slow != 0;
+                    if (slow) vdim_row = -1;
+                }
+                const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
+                const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
+                unsigned char* tv = smem + P::OFF_V + s * P::V_BYTES;
+                if (ok) {
+                    if (v_exact) {
+                        if (vb == 8) codes_tile<8, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
+                        else if (vb == 4) codes_tile<4, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
+                        else codes_tile<2, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
+                    } else if (!slow && v_grouped) {
+                        if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                        else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                        else group_tile<2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                    } else if (!slow && v_perdim) {
+                        if (vb == 8) perdim_tile<8>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, VTHR, vrows);
+                        else if (vb == 4) perdim_tile<4>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, VTHR, vrows);
+                        else perdim_tile<2>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, VTHR, vrows);
+                    } else {
+                        if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                        else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                        else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                    }
+                    // normaliser columns D .. D + 15 of every key of the tile: 2^-6 / V scale and 2^-8 * V zero-point as fp16 hi + lo
+                    // pairs, twelve zeros (every row gets finite values: P is zero for the keys past the end, but 0 * NaN is not)
+    #pragma unroll
+                    for (int i = 0; i < KPT; ++i) {
+                        const int kt = ptid + i * VTHR;
+                        if (kt < N) {
+                            const float vin = TC_AUX_DOWN * __frcp_rn(fmaxf(vs[i], TC_VS_MIN)), vzd = vz[i] * TC_ZP_DOWN;
+                            const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
+                            const __half vin_lo = __float2half_rn(vin - __half2float(vin_hi)), vz_lo = __float2half_rn(vzd - __half2float(vz_hi));
+                            unsigned char* ax = tv + vtile_off(kt, D, N);
+                            sts128(ax, (uint32_t)__half_as_ushort(vin_hi) | ((uint32_t)__half_as_ushort(vin_lo) << 16),
+                                   (uint32_t)__half_as_ushort(vz_hi) | ((uint32_t)__half_as_ushort(vz_lo) << 16), 0u, 0u);
+                            sts128(ax + N * 16, 0u, 0u, 0u, 0u);
+                        }
+                    }
+                    fence_async_smem();
+                    mbar_arrive(&bar_v[s]);
+                }
+
+                {
+                    uint32_t all_ok;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(all_ok) : "r"((uint32_t)ok), "n"(VTHR) : "memory");
+                    ok = all_ok != 0;
+                }
+                if (!ok) break;
+                if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
             }
-            ok = ok && mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
-            if (j >= 2) ok = ok && mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
-            if (v_grouped || v_perdim) {   // tables visible to all producers; they agree on the converter
-                uint32_t any_slow;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(any_slow) : "r"((uint32_t)slow) : "memory");
-                slow = any_slow != 0;
-                if (slow) vdim_row = -1;
+            if (!ok && ptid == 0) {
+                for (int j = 0; j < issued; ++j) {
+                    bool landed = false;
+                    for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pkv[j & 1], (j >> 1) & 1);
+                }
             }
-            const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
-            const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
-            unsigned char* tv = smem + P::OFF_V + s * P::V_BYTES;
-            if (ok) {
+        } else {
+            // =============================================================== V converters
+            const int ptid = tid - R::V_WARP0 * 32;
+            const bool v_exact = a.vp.group == D;
+            const bool v_grouped = a.prep_vrec_bytes > 0;                    // records for the packed-half converter were prepared
+            const int v_ng = D / a.vp.group;
+            const int v_gshift = __ffs(v_ng) - 1, v_grp_shift = __ffs(a.vp.group) - 1;
+            const ParamRef* v_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF + 48);
+            if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF + 48) = param_ref(a.vp, b, h);
+            asm volatile("bar.sync 2, %0;" ::"n"(VTHR) : "memory");
+            for (int j = 0; j < T; ++j) {
+                const int s = j & 1;
+                const int n_valid = tile_n(j);
+                bool ok = mbar_wait(&bar_pkv[s], (j >> 1) & 1, abort_flag, 24);
+                if (ok && j >= 2) ok = mbar_wait(&bar_pv[s], ((j - 2) >> 1) & 1, abort_flag, 23);   // V stage is free
+                if (!ok) break;
+                const uint32_t* pv = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s + 1) * P::PK_BYTES);
+                const int vrows = min(N, (n_valid + 15) & ~15);     // the PV product stops at the 16-key step that holds the last key
+                unsigned char* tv = smem + P::OFF_V + s * P::V_BYTES;
                 if (v_exact) {
-                    if (vb == 8) codes_tile<8, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else if (vb == 4) codes_tile<4, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else codes_tile<2, true>(tv, pv, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                } else if (!slow && v_grouped) {
-                    if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
-                    else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
-                    else group_tile<2>(tv, pv, vpar, n_valid, N, wv, ptid, TC_VPROD, vrows, v_gshift, v_grp_shift);
-                } else if (!slow && v_perdim) {
-                    if (vb == 8) perdim_tile<8>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else if (vb == 4) perdim_tile<4>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
-                    else perdim_tile<2>(tv, pv, vdim_s, vdim_sl, vdim_zb, n_valid, N, wv, ptid, TC_VPROD, vrows);
+                    if (vb == 8) codes_tile<8, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
+                    else if (vb == 4) codes_tile<4, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
+                    else codes_tile<2, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
                 } else {
-                    if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
-                    else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
-                    else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, TC_VPROD);
+                    const uint2* vpar = reinterpret_cast<const uint2*>(smem + (s ? P::OFF_VRAW : P::OFF_VPAR));
+                    const bool slow = !v_grouped || reinterpret_cast<const uint32_t*>(vpar + (N << v_gshift))[0] != 0u;
+                    if (!slow) {
+                        if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                        else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                        else group_tile<2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                    } else {
+                        const int k0 = tile_k0(j);
+                        if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                        else if (vb == 4) dequant_tile<4>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                        else dequant_tile<2>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
+                    }
                 }
                 // normaliser columns D .. D + 15 of every key of the tile: 2^-6 / V scale and 2^-8 * V zero-point as fp16 hi + lo
-                // pairs, twelve zeros (every row gets finite values: P is zero for the keys past the end, but 0 * NaN is not)
-#pragma unroll
-                for (int i = 0; i < KPT; ++i) {
-                    const int kt = ptid + i * TC_VPROD;
-                    if (kt < N) {
-                        const float vin = TC_AUX_DOWN * __frcp_rn(fmaxf(vs[i], TC_VS_MIN)), vzd = vz[i] * TC_ZP_DOWN;
-                        const __half vin_hi = __float2half_rn(vin), vz_hi = __float2half_rn(vzd);
-                        const __half vin_lo = __float2half_rn(vin - __half2float(vin_hi)), vz_lo = __float2half_rn(vzd - __half2float(vz_hi));
-                        unsigned char* ax = tv + vtile_off(kt, D, N);
-                        sts128(ax, (uint32_t)__half_as_ushort(vin_hi) | ((uint32_t)__half_as_ushort(vin_lo) << 16),
-                               (uint32_t)__half_as_ushort(vz_hi) | ((uint32_t)__half_as_ushort(vz_lo) << 16), 0u, 0u);
-                        sts128(ax + N * 16, 0u, 0u, 0u, 0u);
-                    }
+                // pairs (prepared per key), twelve zeros
+                const uint2* vn = reinterpret_cast<const uint2*>(smem + P::OFF_VNST) + s * N;
+                for (int kt = ptid; kt < N; kt += VTHR) {
+                    const uint2 r = vn[kt];
+                    unsigned char* ax = tv + vtile_off(kt, D, N);
+                    sts128(ax, r.x, r.y, 0u, 0u);
+                    sts128(ax + N * 16, 0u, 0u, 0u, 0u);
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_v[s]);
             }
-
-            {
-                uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 96, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"((uint32_t)ok) : "memory");
-                ok = all_ok != 0;
-            }
-            if (!ok) break;
-            if (ptid == 0 && j + 2 < T) { issue(j + 2); ++issued; }
         }
-        if (!ok && ptid == 0) {
-            for (int j = 0; j < issued; ++j) {
-                bool landed = false;
-                for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i) landed = mbar_try(&bar_pkv[j & 1], (j >> 1) & 1);
-            }
-        }
-    } else if (lane == 0) {
+    } else if (warp == MMA_WARP && lane == 0) {
         // =============================================================== MMA issue (one thread of warp 15)
         // Order: S(0), S(1), then per tile j: wait P(j) -> S(j+2) -> O += P(j) V(j).  S(j+2) reuses the TMEM
         // columns of S(j), free once P(j) is complete, and goes first because the softmax two tiles ahead
@@ -1420,9 +1645,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(AttnArgs a, int 
         }
         if (ok) tc_commit(bar_o);
         tc_fence_before();
+    } else if (!QF && warp == R::LOAD_WARP) {
+        // =============================================================== copy issue (one thread)
+        // Tile t goes into the stages of tile t - 2 once the converters have arrived on that tile's operand barriers (their
+        // last read of the packed stage).  The table slot of tile t was last read by the softmax of tile t - 8: K(t - 2)
+        // converted means S(t - 4) is complete, which was issued after P(t - 6).
+        if (lane == 0) {
+            bool ok = true;
+            int issued = min(T, 2);
+            for (int t = 2; t < T && ok; ++t) {
+                const int s = t & 1;
+                const uint32_t par = ((t - 2) >> 1) & 1;
+                bool kd = false, vd = false;
+                uint32_t tries = 0;
+                while (true) {
+                    if (!kd && mbar_try(&bar_k[s], par)) { issue_k(t); kd = true; }
+                    if (!vd && mbar_try(&bar_v[s], par)) { issue_v(t); vd = true; }
+                    if (kd && vd) break;
+                    if (*abort_flag) { ok = false; break; }
+                    if (++tries >= TC_SPIN_LIMIT) {
+                        *abort_flag = 1;
+                        atomicCAS(&g_tc_status, 0, 41);
+                        ok = false;
+                        break;
+                    }
+                }
+                if (kd || vd) issued = t + 1;
+            }
+            if (!ok || *abort_flag) {
+                // drain: bulk copies already issued must land before the CTA may exit
+                for (int t = max(0, issued - 2); t < issued; ++t) {
+                    bool landed = false;
+                    for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i)
+                        landed = mbar_try(&bar_pk[t & 1], (t >> 1) & 1) && mbar_try(&bar_pkv[t & 1], (t >> 1) & 1) &&
+                                 mbar_try(&bar_t[t & (P::TAB_SLOTS - 1)], (t / P::TAB_SLOTS) & 1);
+                }
+            }
+        }
     }
     __syncthreads();
-    if (warp == 15) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P::TMEM_COLS) : "memory");
     }
@@ -1438,10 +1700,49 @@ bool attn_tc_eligible(const AttnArgs& a, int kb, int vb) {
     return true;
 }
 
+// Records for the packed-half converters exist when the groups are a power of two of whole packed words and a tile's records fit
+// their staging buffer (with the trailer): at most 256 (key, group) pairs per tile.
+static bool records_apply(int group, int D, int bits, int N) {
+    const int vpw = 32 / bits, ng = D / group;
+    return group != D && (group % vpw) == 0 && (group & (group - 1)) == 0 && N * ng <= 256;
+}
+static size_t prep_tile_bytes_max(int N) { return (size_t)3 * N * 4 + (size_t)N * 8 + 2 * (256 * 8 + 16); }
+
+size_t attn_tc_workspace_bytes(int B, int H, int Lk, int D) {
+    if (D != 64 && D != 128) return 0;
+    const int N = D == 64 ? 128 : 64;
+    const size_t tiles = (size_t)(Lk + N - 1) / N;
+    return (size_t)B * H * tiles * prep_tile_bytes_max(N) + 256;       // + room to align the base
+}
+
 template <int D, int NQ, int KM>
-static int launch_tc(const AttnArgs& a0, int kb, int vb, cudaStream_t st) {
+static int launch_tc(const AttnArgs& a0, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st) {
     AttnArgs a = a0;
     using P = TcPlan<D, NQ, KM>;
+    if constexpr (KM != KM_FOLD) {
+        constexpr int N = P::N;
+        const int T = (a.Lk + N - 1) / N;
+        const bool k_rec = KM == KM_SPLIT && records_apply(a.kp.group, D, kb, N);
+        const bool v_rec = records_apply(a.vp.group, D, vb, N);
+        const int k_ng = D / a.kp.group, v_ng = D / a.vp.group;
+        a.prep_off_vn = P::TAB_ROWS * N * 4;
+        a.prep_off_krec = a.prep_off_vn + N * 8;
+        a.prep_krec_bytes = k_rec ? N * k_ng * 8 + 16 : 0;
+        a.prep_off_vrec = a.prep_off_krec + a.prep_krec_bytes;
+        a.prep_vrec_bytes = v_rec ? N * v_ng * 8 + 16 : 0;
+        a.prep_tile_stride = a.prep_off_vrec + a.prep_vrec_bytes;
+        a.prep_bh_stride = (long long)T * a.prep_tile_stride;
+        const uintptr_t base = (reinterpret_cast<uintptr_t>(ws) + 255) & ~(uintptr_t)255;
+        const size_t need = (size_t)a.B * a.H * (size_t)a.prep_bh_stride + (base - reinterpret_cast<uintptr_t>(ws));
+        if (!ws || ws_bytes < need)
+            return fail(VARQ_ERR_WORKSPACE, "varq_attn_fwd: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+        a.prep = reinterpret_cast<unsigned char*>(base);
+        const long long prep_blocks = (long long)a.B * a.H * T;
+        if (prep_blocks > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
+        tc_prepare_kernel<N><<<(unsigned)prep_blocks, N, 0, st>>>(a, T, KM == KM_SPLIT ? 1 : 0, k_ng, v_ng, kb, vb);
+        VARQ_CUDA_TRY(cudaGetLastError());
+        count_launches(1);
+    }
     static_assert(P::TOTAL + 1024 <= 227 * 1024, "shared-memory plan exceeds the per-CTA limit");
     const size_t smem = P::TOTAL + 1024;   // slack for the 1024-byte alignment of the swizzled tiles
     static bool configured[64] = {false};    // per device; the attribute is sticky, set it outside any stream capture
@@ -1455,13 +1756,13 @@ static int launch_tc(const AttnArgs& a0, int kb, int vb, cudaStream_t st) {
     const long long blocks_1d = (long long)a.B * a.H * nqt;
     if (blocks_1d > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
     a.n_qtiles = nqt;
-    attn_tc_kernel<D, NQ, KM><<<(unsigned)blocks_1d, TC_THREADS, smem, st>>>(a, kb, vb);
+    attn_tc_kernel<D, NQ, KM><<<(unsigned)blocks_1d, TcRoles<KM>::THREADS, smem, st>>>(a, kb, vb);
     VARQ_CUDA_TRY(cudaGetLastError());
     count_launches(1);
     return VARQ_OK;
 }
 
-int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
+int attn_tc_run(const AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st) {
     // fp16 queries, and bf16 queries inside fp16's normal range (2^-14 <= |q| <= 65504), are exact in one fp16 term;
     // larger magnitudes saturate, smaller ones lose low bits (both far outside what a softmax can resolve)
     const bool split_q = a.q_dtype == VARQ_F32;
@@ -1471,13 +1772,13 @@ int attn_tc_run(const AttnArgs& a, int kb, int vb, cudaStream_t st) {
     const bool fold = varies && a.kp.row_of_token && a.kp.row_begin && a.kp.n_rows > 0 && a.kp.n_rows <= 0xffff &&
                       (a.Lk + n_max - 1) / n_max + a.kp.n_rows <= TC_MAX_TILES;
     if (a.D == 64) {
-        if (fold) return launch_tc<64, 2, KM_FOLD>(a, kb, vb, st);
-        if (varies) return split_q ? launch_tc<64, 2, KM_SPLIT>(a, kb, vb, st) : launch_tc<64, 1, KM_SPLIT>(a, kb, vb, st);
-        return split_q ? launch_tc<64, 2, KM_EXACT>(a, kb, vb, st) : launch_tc<64, 1, KM_EXACT>(a, kb, vb, st);
+        if (fold) return launch_tc<64, 2, KM_FOLD>(a, kb, vb, ws, ws_bytes, st);
+        if (varies) return split_q ? launch_tc<64, 2, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st) : launch_tc<64, 1, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st);
+        return split_q ? launch_tc<64, 2, KM_EXACT>(a, kb, vb, ws, ws_bytes, st) : launch_tc<64, 1, KM_EXACT>(a, kb, vb, ws, ws_bytes, st);
     }
-    if (fold) return launch_tc<128, 2, KM_FOLD>(a, kb, vb, st);
-    if (varies) return split_q ? launch_tc<128, 2, KM_SPLIT>(a, kb, vb, st) : launch_tc<128, 1, KM_SPLIT>(a, kb, vb, st);
-    return split_q ? launch_tc<128, 2, KM_EXACT>(a, kb, vb, st) : launch_tc<128, 1, KM_EXACT>(a, kb, vb, st);
+    if (fold) return launch_tc<128, 2, KM_FOLD>(a, kb, vb, ws, ws_bytes, st);
+    if (varies) return split_q ? launch_tc<128, 2, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st) : launch_tc<128, 1, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st);
+    return split_q ? launch_tc<128, 2, KM_EXACT>(a, kb, vb, ws, ws_bytes, st) : launch_tc<128, 1, KM_EXACT>(a, kb, vb, ws, ws_bytes, st);
 }
 
 int attn_tc_status(int* out) {
