@@ -31,8 +31,8 @@ namespace varq {
 // latency-bound (a warp retires an instruction every ~6 cycles), so the conversion of a tile is spread over many of them;
 // the folded-query mode keeps 4 + 3 because its K producers own one query row each.
 template <int KM> struct TcRoles {
-    static constexpr int KW = 4;
-    static constexpr int VW = 3;
+    static constexpr int KW = KM == 1 ? 6 : 4;            // measured: a dequantised K (two operand tiles) wants more K converters
+    static constexpr int VW = KM == 2 ? 3 : KM == 1 ? 4 : 6;            // 20 warps keep 96 registers per thread
     static constexpr int KTHR = KW * 32, VTHR = VW * 32;
     static constexpr int K_WARP0 = 8, V_WARP0 = 8 + KW, MMA_WARP = 8 + KW + VW;
     static constexpr int LOAD_WARP = MMA_WARP + 1;        // issues the bulk copies (not in the folded-query mode)
@@ -105,14 +105,21 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// Both are called by every lane of the MMA warp with the same operands and executed by one elected lane: the warp stays
+// converged, so the descriptors are computed once in uniform registers, which is where the instruction takes them from.
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -866,7 +873,10 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + P::OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + P::OFF_MISC + 4);
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // the warp index through a shuffle: the compiler then knows that it is the same in every lane, keeps the role branches
+    // uniform and can hold addresses, descriptors and loop counters of a role in uniform registers
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     // query tile fastest: the tiles of one (sample, head) run together and share its packed rows in L2
     const int qt = (int)(blockIdx.x % (unsigned)a.n_qtiles), bh = (int)(blockIdx.x / (unsigned)a.n_qtiles), b = bh / a.H, h = bh - b * a.H;
     const int q0 = qt * TC_M;
@@ -1556,14 +1566,18 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                 mbar_arrive(&bar_v[s]);
             }
         }
-    } else if (warp == MMA_WARP && lane == 0) {
-        // =============================================================== MMA issue (one thread of warp 15)
+    } else if (warp == MMA_WARP) {
+        // =============================================================== MMA issue (the whole warp waits; one elected lane issues)
         // Order: S(0), S(1), then per tile j: wait P(j) -> S(j+2) -> O += P(j) V(j).  S(j+2) reuses the TMEM
         // columns of S(j), free once P(j) is complete, and goes first because the softmax two tiles ahead
         // waits for it while nobody waits for the accumulator.
         constexpr uint32_t IDESC_S = instr_desc(TC_M, N, 0);
         constexpr uint32_t IDESC_O = instr_desc(TC_M, D + 16, 1);     // output columns and normaliser columns in one product
         bool ok = true;
+        // every lane waits; the lanes agree on the outcome so that the warp stays converged for the elected instructions
+        auto wait_all = [&](uint64_t* bar, uint32_t parity, int code) -> bool {
+            return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, code));
+        };
         // descriptors differ from their stage base only in the start-address field (bits 0-13, 16-byte units)
         const uint64_t qd0 = smem_desc(smem_u32(smem + P::OFF_Q), 16, 1024);
         const uint64_t kd0 = smem_desc(smem_u32(smem + P::OFF_K), 16, 1024);
@@ -1573,7 +1587,7 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
         // S = Q K^T of tile j.  exact-code K: Q_hi K [+ Q_lo K]; dequantised K: Q_hi K_hi + Q_hi K_lo [+ Q_lo K_hi]
         auto issue_qk = [&](int j) -> bool {
             const int s = j & 1;
-            if (!mbar_wait(&bar_k[s], (j >> 1) & 1, abort_flag, 31)) return false;
+            if (!wait_all(&bar_k[s], (j >> 1) & 1, 31)) return false;
             tc_fence_after();
             const uint64_t kd = kd0 + (uint64_t)((s * P::KT * P::KV_BYTES) >> 4);
             bool first = true;
@@ -1622,12 +1636,12 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
         for (int jj = 0; jj < T + 2 && ok; ++jj) {
             const int j = jj - 2;
             if (j >= 0) {
-                ok = mbar_wait(&bar_p[j & 1], (j >> 1) & 1, abort_flag, 32);
+                ok = wait_all(&bar_p[j & 1], (j >> 1) & 1, 32);
                 if (!ok) break;
                 tc_fence_after();
             }
             if (P::PST == 1 && j >= 0) {
-                ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, 34);
+                ok = wait_all(&bar_v[j & 1], (j >> 1) & 1, 34);
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(j);
@@ -1637,7 +1651,7 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                 if (!ok) break;
             }
             if (P::PST == 2 && j >= 0) {
-                ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, 34);
+                ok = wait_all(&bar_v[j & 1], (j >> 1) & 1, 34);
                 if (!ok) break;
                 tc_fence_after();
                 issue_pv(j);
@@ -1652,33 +1666,30 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
         // converted means S(t - 4) is complete, which was issued after P(t - 6).
         if (lane == 0) {
             bool ok = true;
-            int issued = min(T, 2);
-            for (int t = 2; t < T && ok; ++t) {
-                const int s = t & 1;
-                const uint32_t par = ((t - 2) >> 1) & 1;
-                bool kd = false, vd = false;
-                uint32_t tries = 0;
-                while (true) {
-                    if (!kd && mbar_try(&bar_k[s], par)) { issue_k(t); kd = true; }
-                    if (!vd && mbar_try(&bar_v[s], par)) { issue_v(t); vd = true; }
-                    if (kd && vd) break;
-                    if (*abort_flag) { ok = false; break; }
-                    if (++tries >= TC_SPIN_LIMIT) {
-                        *abort_flag = 1;
-                        atomicCAS(&g_tc_status, 0, 41);
-                        ok = false;
-                        break;
-                    }
+            int tk = min(T, 2), tv = min(T, 2);          // next tile of each stream (the first two were requested during set-up)
+            uint32_t tries = 0;
+            while (tk < T || tv < T) {
+                bool progress = false;
+                if (tk < T && mbar_try(&bar_k[tk & 1], ((tk - 2) >> 1) & 1)) { issue_k(tk); ++tk; progress = true; }
+                if (tv < T && mbar_try(&bar_v[tv & 1], ((tv - 2) >> 1) & 1)) { issue_v(tv); ++tv; progress = true; }
+                if (progress) { tries = 0; continue; }
+                if (*abort_flag) { ok = false; break; }
+                if (++tries >= TC_SPIN_LIMIT) {
+                    *abort_flag = 1;
+                    atomicCAS(&g_tc_status, 0, 41);
+                    ok = false;
+                    break;
                 }
-                if (kd || vd) issued = t + 1;
             }
+            const int issued = max(tk, tv);
             if (!ok || *abort_flag) {
                 // drain: bulk copies already issued must land before the CTA may exit
                 for (int t = max(0, issued - 2); t < issued; ++t) {
                     bool landed = false;
                     for (uint32_t i = 0; i < TC_SPIN_LIMIT && !landed; ++i)
-                        landed = mbar_try(&bar_pk[t & 1], (t >> 1) & 1) && mbar_try(&bar_pkv[t & 1], (t >> 1) & 1) &&
-                                 mbar_try(&bar_t[t & (P::TAB_SLOTS - 1)], (t / P::TAB_SLOTS) & 1);
+                        landed = (t >= tk || (mbar_try(&bar_pk[t & 1], (t >> 1) & 1) &&
+                                              mbar_try(&bar_t[t & (P::TAB_SLOTS - 1)], (t / P::TAB_SLOTS) & 1))) &&
+                                 (t >= tv || mbar_try(&bar_pkv[t & 1], (t >> 1) & 1));
                 }
             }
         }
