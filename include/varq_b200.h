@@ -195,7 +195,10 @@ int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_t L, int32_
 #define VARQ_ATTN_PATH_TC     3
 int varq_attn_force_path(int32_t path);
 
-/* Bytes of scratch varq_attn_fwd needs (partial results of the key-split path). */
+/* Bytes of scratch varq_attn_fwd needs for this shape, whichever kernel it picks: partial results of the
+ * key-split CUDA-core kernels, or the per-tile parameter streams that the tensor-core kernel's preparation launch
+ * writes (about 8 KB per 64 or 128 cached tokens of every (sample, head); sized for the widest grouping).
+ * varq_attn_fwd fails with VARQ_ERR_WORKSPACE when given less. */
 size_t varq_attn_workspace_bytes(int32_t B, int32_t H, int32_t Lq, int32_t Lk, int32_t D,
                                  int32_t k_store_bits, int32_t v_store_bits);
 

@@ -1,21 +1,27 @@
 // Attention over the packed cache on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
 //
-// One CTA = one (sample, head) x 128 queries, looping over key tiles.  Sixteen warps:
-//   warps 0-7  softmax: two threads share query row r (TMEM lane r), each owning half of every
-//              tile's keys AND its own output accumulator, so the pair never has to agree on a
-//              running maximum: a thread reads its S columns from TMEM 32 at a time, applies the
-//              per-key scale / zero-point of K, exponentiates against its own lazily updated
-//              reference maximum and writes P (fp16) to shared memory.  The two partial results
-//              of a row are merged once, in the epilogue;
-//   warps 8-11 (K) and 12-14 (V) producers: bulk-async-copy (TMA engine, 1-D) the packed K and V rows of a tile into
-//              shared memory, dequantise them there into UMMA operand tiles (128B-swizzled):
-//              K as exact fp16 integer codes, V as fp16 (code - zp) * scale; the K producers also
-//              write the per-key tables, the V producers a small operand tile holding 1 / V-scale
-//              and the V zero-point of each key (fp16 hi + lo pairs);
-//   warp  15   one thread issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM),
-//              O_half += P V and, with the small tile as B operand, the softmax normaliser
-//              and zero-point correction sum_k P (the tensor core adds up exactly the rounded P
-//              that it multiplies with V), and commits completion to mbarriers.
+// Two launches per call.  A small preparation kernel turns the per-key quantisation parameters of one (sample, head) into
+// ready-made streams, one block per key tile: the softmax tables, the normaliser record of every key and, where the
+// packed-half converters apply, the (key, group) records of K and V.  The main kernel then never loads a parameter from
+// global memory with an ordinary load: everything a tile needs arrives by 1-D bulk copies (TMA engine) on mbarriers.
+//
+// Main kernel: one CTA = one (sample, head) x 128 queries, looping over key tiles.  Warps:
+//   0-7        softmax: two threads share query row r (TMEM lane r), each owning half of every tile's keys AND its own
+//              output accumulator, so the pair never has to agree on a running maximum: a thread reads its S columns from
+//              TMEM 32 at a time, applies the per-key scale / zero-point of K, exponentiates against its own lazily
+//              updated reference maximum and writes P (fp16) to shared memory.  The two partial results of a row are
+//              merged once, in the epilogue;
+//   K and V converters (TcRoles: 4 + 6, or 6 + 4 when K is dequantised): wait for a tile's packed rows, turn them into
+//              UMMA operand tiles in shared memory and arrive.  K: exact fp16 integer codes (128B-swizzled, K-major), or an
+//              fp16 hi + lo pair of (code - zp) * scale when the scale varies along head_dim per key.  V: unswizzled
+//              MN-major tile of D + 16 columns, codes or (code - zp) * scale, whose last 16 columns carry 1 / V-scale and
+//              the V zero-point of each key (fp16 hi + lo pairs);
+//   MMA warp   waits converged; one elected lane issues tcgen05.mma: S = Q K^T (fp16 x fp16 -> fp32 in TMEM) and
+//              (O_half | normaliser sums) += P (V | normaliser columns), so the tensor core adds up exactly the rounded P that
+//              it multiplies with V, and commits completion to mbarriers;
+//   copy warp  one thread requests tile t + 2 of each stream as soon as the converters have arrived for tile t.
+// In the folded-query mode (per-dim K scales that are constant over the tokens of an appended step) the older arrangement is
+// kept: 4 + 3 producer warps that also fetch parameters, write the tables and request their own copies, and no copy warp.
 // Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
 // no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
 // rounded to fp16 (bf16 would miss the 1e-3 relative-L2 target by 10x).  A V scale below 2^-20
@@ -27,9 +33,10 @@
 
 namespace varq {
 
-// Warp roles of a CTA: 8 softmax warps, KW K-producer warps, VW V-producer warps, then the MMA warp.  The producers are
-// latency-bound (a warp retires an instruction every ~6 cycles), so the conversion of a tile is spread over many of them;
-// the folded-query mode keeps 4 + 3 because its K producers own one query row each.
+// Warp roles of a CTA: 8 softmax warps, KW K-converter warps, VW V-converter warps, the MMA warp, the copy-issue warp.
+// The converters are latency-bound (a warp retires an instruction every 6 to 10 cycles), so a tile is spread over as many
+// of them as fit: 20 warps keep 96 registers per thread, the next allocation step (24 warps, 80 registers) measured slower.
+// The folded-query mode keeps 4 + 3 because its K producers own one query row each.
 template <int KM> struct TcRoles {
     static constexpr int KW = KM == 1 ? 6 : 4;            // measured: a dequantised K (two operand tiles) wants more K converters
     static constexpr int VW = KM == 2 ? 3 : KM == 1 ? 4 : 6;            // 20 warps keep 96 registers per thread
@@ -992,31 +999,42 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
         constexpr int CH = D / 8;   // 16-byte chunks per row
         const int qtid = warp < 8 ? tid : 256 + lane;
         const bool want_qsum = !KS && a.kp.zp != nullptr;
-        for (int i = qtid; i < TC_M * CH; i += 288) {
-            const int r = i / CH, c = i - r * CH;
-            float v[8];
+        // four chunks per thread in flight: the loads of a batch are all issued before the first one is used
+        constexpr int QB = 4;
+#pragma unroll 1
+        for (int i0 = qtid; i0 < TC_M * CH; i0 += QB * 288) {
+            float v[QB][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.f;
-            if (r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v);
-            // the operand is fp16: a query element beyond its range (an fp32 or bf16 value above 65504) saturates instead
-            // of becoming infinite
+            for (int u = 0; u < QB; ++u) {
+                const int i = i0 + u * 288, r = i / CH, c = i - r * CH;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = fminf(fmaxf(v[j], -65504.f), 65504.f);
-            uint32_t hi[4], lo[4];
-            float part = 0.f;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                const float2 hf = __half22float2(h);
-                const __half2 l = __floats2half2_rn(v[2 * j] - hf.x, v[2 * j + 1] - hf.y);
-                hi[j] = *reinterpret_cast<const uint32_t*>(&h);
-                lo[j] = *reinterpret_cast<const uint32_t*>(&l);
-                part += v[2 * j] + v[2 * j + 1];
+                for (int j = 0; j < 8; ++j) v[u][j] = 0.f;
+                if (i < TC_M * CH && r < nq) load_q8(a.q, a.q_dtype, b * a.qs_b + (long long)(q0 + r) * a.qs_l + h * a.qs_h + c * 8, v[u]);
             }
-            const uint32_t off = tile_off(r, c * 8, TC_M);
-            sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
-            if constexpr (NQ == 2) sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
-            if (want_qsum && r < nq) atomicAdd(&s_qsum[r], part);
+#pragma unroll
+            for (int u = 0; u < QB; ++u) {
+                const int i = i0 + u * 288, r = i / CH, c = i - r * CH;
+                if (i >= TC_M * CH) break;
+                // the operand is fp16: a query element beyond its range (an fp32 or bf16 value above 65504) saturates instead
+                // of becoming infinite
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[u][j] = fminf(fmaxf(v[u][j], -65504.f), 65504.f);
+                uint32_t hi[4], lo[4];
+                float part = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 h = __floats2half2_rn(v[u][2 * j], v[u][2 * j + 1]);
+                    const float2 hf = __half22float2(h);
+                    const __half2 l = __floats2half2_rn(v[u][2 * j] - hf.x, v[u][2 * j + 1] - hf.y);
+                    hi[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    lo[j] = *reinterpret_cast<const uint32_t*>(&l);
+                    part += v[u][2 * j] + v[u][2 * j + 1];
+                }
+                const uint32_t off = tile_off(r, c * 8, TC_M);
+                sts128(smem + P::OFF_Q + off, hi[0], hi[1], hi[2], hi[3]);
+                if constexpr (NQ == 2) sts128(smem + P::OFF_Q + P::Q_BYTES + off, lo[0], lo[1], lo[2], lo[3]);
+                if (want_qsum && r < nq) atomicAdd(&s_qsum[r], part);
+            }
         }
         fence_async_smem();
         asm volatile("bar.sync 7, 288;" ::: "memory");
@@ -1555,8 +1573,9 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                 }
                 // normaliser columns D .. D + 15 of every key of the tile: 2^-6 / V scale and 2^-8 * V zero-point as fp16 hi + lo
                 // pairs (prepared per key), twelve zeros
+                // (by the highest-numbered threads: they have the fewest items to convert)
                 const uint2* vn = reinterpret_cast<const uint2*>(smem + P::OFF_VNST) + s * N;
-                for (int kt = ptid; kt < N; kt += VTHR) {
+                for (int kt = VTHR - 1 - ptid; kt < N; kt += VTHR) {
                     const uint2 r = vn[kt];
                     unsigned char* ax = tv + vtile_off(kt, D, N);
                     sts128(ax, r.x, r.y, 0u, 0u);
