@@ -338,40 +338,49 @@ template <bool KEYMAJ> struct ItemWalk {
     }
 };
 
-// Exact-code operand tile: each thread converts 16 bytes (4 words) of one key at a time.
-template <int BITS, bool VL = false>      // VL: the unswizzled V layout
+// An item = IW consecutive packed words of one key (IW = 4 or 2), converted by one thread per trip.  The dequantising
+// converters take half-size items when those spread a tile over the threads more evenly (see finer_items); for the exact-code
+// converter the extra trips cost more than the balance gains (measured).
+template <int IW> __device__ __forceinline__ void lds_words(const uint32_t* p, uint32_t (&w)[IW]) {
+    if constexpr (IW == 4) { const uint4 v = lds128(p); w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+    else { const uint2 v = *reinterpret_cast<const uint2*>(p); w[0] = v.x; w[1] = v.y; }
+}
+// true if items of two words need fewer half-item trips per thread than items of four
+__device__ __forceinline__ bool finer_items(int items4, int nthr) {
+    return (2 * items4 + nthr - 1) / nthr < 2 * ((items4 + nthr - 1) / nthr);
+}
+// Exact-code operand tile.
+template <int BITS, bool VL = false, int IW = 4>      // VL: the unswizzled V layout
 __device__ __noinline__ void codes_tile(unsigned char* tile, const uint32_t* packed, int n_valid, int N, int W, int ptid, int nthr = 128,
                                            int rows = -1) {
     // rows [n_valid, rows) are zero-filled; consumers never read past `rows`
     if (rows < 0) rows = N;
     constexpr int VPW = 32 / BITS;            // codes per word
     constexpr int HW = VPW / 2;               // 32-bit half2 registers per word
-    ItemWalk<(BITS < 8)> wk;      // measured: 8-bit rows (64 or 128 bytes per key) convert faster item by item
+    ItemWalk<(BITS < 8) && VL> wk;      // measured: key by key only pays for the unswizzled V tile below 8 bits
 #pragma unroll 1
-    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
-        const int key = wk.key, wi = wk.item << 2;
-        uint4 pk = make_uint4(0u, 0u, 0u, 0u);
-        uint32_t h[4 * HW];
+    for (wk.init(ptid, rows, W / IW, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item * IW;
+        uint32_t h[IW * HW];
         if (key < n_valid) {
-            pk = lds128(packed + key * W + wi);
-            codes_cvt<BITS>(pk.x, h);
-            codes_cvt<BITS>(pk.y, h + HW);
-            codes_cvt<BITS>(pk.z, h + 2 * HW);
-            codes_cvt<BITS>(pk.w, h + 3 * HW);
+            uint32_t wd[IW];
+            lds_words<IW>(packed + key * W + wi, wd);
+#pragma unroll
+            for (int q = 0; q < IW; ++q) codes_cvt<BITS>(wd[q], h + q * HW);
         } else {
 #pragma unroll
-            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+            for (int i = 0; i < IW * HW; ++i) h[i] = 0u;
         }
         const int d0 = wi * VPW;              // first head_dim index of the item
         if constexpr (VL) {
             unsigned char* base = tile + vtile_off(key, d0, N);
 #pragma unroll
-            for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+            for (int c = 0; c < IW * HW / 4; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
         } else {
             unsigned char* row = tile + (d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128;
             const int ch0 = (d0 & 63) >> 3;
 #pragma unroll
-            for (int c = 0; c < HW; ++c)         // HW chunks of 8 halves
+            for (int c = 0; c < IW * HW / 4; ++c)         // chunks of 8 halves
                 sts128(row + (((ch0 + c) ^ (key & 7)) << 4), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
         }
     }
@@ -550,21 +559,21 @@ template <int MAXE> struct ParStage {
     }
 };
 
-// K: hi + lo operand tiles from the staged records; each thread converts 16 bytes (4 words) of one key at a time.
-template <int BITS>
+// K: hi + lo operand tiles from the staged records.
+template <int BITS, int IW = 4>
 __device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed, const uint2* par,
                                               int n_valid, int N, int W, int ptid, int nthr, int g_shift, int grp_shift) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
     ItemWalk<false> wk;      // the items of a key share a parameter record: neighbouring lanes read it together
 #pragma unroll 1
-    for (wk.init(ptid, N, W >> 2, nthr); wk.more(); wk.next()) {
-        const int key = wk.key, wi = wk.item << 2;
-        uint32_t hi[4 * HW], lo[4 * HW];
+    for (wk.init(ptid, N, W / IW, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item * IW;
+        uint32_t hi[IW * HW], lo[IW * HW];
         if (key < n_valid) {
-            const uint4 pk = lds128(packed + key * W + wi);
-            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            uint32_t wd[IW];
+            lds_words<IW>(packed + key * W + wi, wd);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < IW; ++q) {
                 const uint2 pr = par[(key << g_shift) + (((wi + q) * VPW) >> grp_shift)];
                 const uint32_t sh = __byte_perm(pr.x, pr.x, 0x1010), sl = __byte_perm(pr.x, pr.x, 0x3232);
                 uint32_t d[HW];
@@ -580,13 +589,13 @@ __device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned c
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 4 * HW; ++i) { hi[i] = 0u; lo[i] = 0u; }
+            for (int i = 0; i < IW * HW; ++i) { hi[i] = 0u; lo[i] = 0u; }
         }
         const int d0 = wi * VPW;
         const uint32_t row = (uint32_t)((d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128);
         const int ch0 = (d0 & 63) >> 3;
 #pragma unroll
-        for (int c = 0; c < HW; ++c) {
+        for (int c = 0; c < IW * HW / 4; ++c) {
             const uint32_t off = row + (((ch0 + c) ^ (key & 7)) << 4);
             sts128(tile_hi + off, hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
             sts128(tile_lo + off, lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
@@ -595,20 +604,20 @@ __device__ __noinline__ void group_split_tile(unsigned char* tile_hi, unsigned c
 }
 
 // V: one operand tile RN((code - zp) * scale) from the staged records (rows [n_valid, rows) zero-filled).
-template <int BITS>
+template <int BITS, int IW = 4>
 __device__ __noinline__ void group_tile(unsigned char* tile, const uint32_t* packed, const uint2* par, int n_valid, int N, int W,
                                         int ptid, int nthr, int rows, int g_shift, int grp_shift) {
     constexpr int VPW = 32 / BITS, HW = VPW / 2;
     ItemWalk<false> wk;
 #pragma unroll 1
-    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
-        const int key = wk.key, wi = wk.item << 2;
-        uint32_t h[4 * HW];
+    for (wk.init(ptid, rows, W / IW, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item * IW;
+        uint32_t h[IW * HW];
         if (key < n_valid) {
-            const uint4 pk = lds128(packed + key * W + wi);
-            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            uint32_t wd[IW];
+            lds_words<IW>(packed + key * W + wi, wd);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < IW; ++q) {
                 const uint2 pr = par[(key << g_shift) + (((wi + q) * VPW) >> grp_shift)];
                 const uint32_t sh = __byte_perm(pr.x, pr.x, 0x1010), sl = __byte_perm(pr.x, pr.x, 0x3232);
                 uint32_t d[HW];
@@ -621,12 +630,12 @@ __device__ __noinline__ void group_tile(unsigned char* tile, const uint32_t* pac
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+            for (int i = 0; i < IW * HW; ++i) h[i] = 0u;
         }
         const int d0 = wi * VPW;
         unsigned char* base = tile + vtile_off(key, d0, N);
 #pragma unroll
-        for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+        for (int c = 0; c < IW * HW / 4; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
     }
 }
 
@@ -1355,6 +1364,7 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
             const bool k_fast = KS && a.prep_krec_bytes > 0;                 // records for the packed-half converter were prepared
             const int k_gshift = __ffs(k_ng) - 1, k_grp_shift = __ffs(a.kp.group) - 1;
             const ParamRef* k_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF);
+            const bool k_fine = finer_items(N * wk / 4, KTHR);               // items of two words spread the tile more evenly
             if constexpr (KS) {
                 if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF) = param_ref(a.kp, b, h);
                 asm volatile("bar.sync 1, %0;" ::"n"(KTHR) : "memory");
@@ -1372,9 +1382,9 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                     // the trailer of the record block says whether a record of the tile is outside the packed-half converter's bounds
                     const bool slow = !k_fast || reinterpret_cast<const uint32_t*>(kpar + (N << k_gshift))[0] != 0u;
                     if (!slow) {
-                        if (kb == 8) group_split_tile<8>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
-                        else if (kb == 4) group_split_tile<4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
-                        else group_split_tile<2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift);
+                        if (kb == 8) { if (k_fine) group_split_tile<8, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<8, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
+                        else if (kb == 4) { if (k_fine) group_split_tile<4, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<4, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
+                        else { if (k_fine) group_split_tile<2, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<2, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
                     } else {
                         const int k0 = tile_k0(j);
                         if (kb == 8) dequant_split_tile<8>(tk, tk + P::KV_BYTES, pk, n_valid, N, wk, ptid, k_ref, k0, KTHR);
@@ -1383,9 +1393,9 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                     }
                 } else {
                     const int krows = min(N, ((n_valid + N / 2 - 1) / (N / 2)) * (N / 2));   // softmax reads whole halves of a tile
-                    if (kb == 8) codes_tile<8>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
-                    else if (kb == 4) codes_tile<4>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
-                    else codes_tile<2>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    if (kb == 8) codes_tile<8, false>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    else if (kb == 4) codes_tile<4, false>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
+                    else codes_tile<2, false>(tk, pk, n_valid, N, wk, ptid, KTHR, krows);
                 }
                 fence_async_smem();
                 mbar_arrive(&bar_k[s]);
@@ -1542,6 +1552,7 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
             const int v_ng = D / a.vp.group;
             const int v_gshift = __ffs(v_ng) - 1, v_grp_shift = __ffs(a.vp.group) - 1;
             const ParamRef* v_ref = reinterpret_cast<const ParamRef*>(smem + P::OFF_PREF + 48);
+            const bool v_fine = finer_items(N * wv / 4, VTHR);
             if (ptid == 0) *reinterpret_cast<ParamRef*>(smem + P::OFF_PREF + 48) = param_ref(a.vp, b, h);
             asm volatile("bar.sync 2, %0;" ::"n"(VTHR) : "memory");
             for (int j = 0; j < T; ++j) {
@@ -1561,9 +1572,9 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                     const uint2* vpar = reinterpret_cast<const uint2*>(smem + (s ? P::OFF_VRAW : P::OFF_VPAR));
                     const bool slow = !v_grouped || reinterpret_cast<const uint32_t*>(vpar + (N << v_gshift))[0] != 0u;
                     if (!slow) {
-                        if (vb == 8) group_tile<8>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
-                        else if (vb == 4) group_tile<4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
-                        else group_tile<2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift);
+                        if (vb == 8) { if (v_fine) group_tile<8, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<8, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
+                        else if (vb == 4) { if (v_fine) group_tile<4, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<4, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
+                        else { if (v_fine) group_tile<2, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<2, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
                     } else {
                         const int k0 = tile_k0(j);
                         if (vb == 8) dequant_tile<8>(tv, pv, n_valid, N, wv, ptid, v_ref, k0, VTHR);
