@@ -147,8 +147,7 @@ def test_groupings_whose_k_scale_varies_along_head_dim(D, q_dtype, kkw, vkw, kb,
     q = torch.randn((B, 169, H, D), generator=torch.Generator().manual_seed(D + kb)).to(q_dtype)
     scale = 1.0 / D ** 0.5
     out, launches = run("tc", q.to(DEV), kq, vq, scale)
-    # per-step K scales are folded into the queries inside the kernel; per-key ones are prepared by a launch of their own
-    assert launches == (1 if km in ("G_SCALE_HEAD_DIM", "G_HEAD_DIM") else 2)
+    assert launches == 2          # per-key (or per-step) parameter preparation + the attention kernel
     check(out, O.attention(q, kd, vd, fmt, scale), f"D={D} {q_dtype} K{kkw} V{vkw} {kb}/{vb}")
 
 
@@ -174,3 +173,23 @@ def test_all_zero_and_tiny_value_tokens_keep_their_attention_weight(D, symmetric
     kd, vd = kr.use_var_q(k), vr.use_var_q(v)
     out, _ = run("tc", q.to(DEV), kq, vq, 1.0 / D ** 0.5)
     check(out, O.attention(q, kd, vd, "BHLc", 1.0 / D ** 0.5).transpose(1, 2), f"zero/tiny V tokens D={D} sym={symmetric}")
+
+
+@pytest.mark.parametrize("D,kb,vb", [(64, 8, 8), (128, 4, 4)])
+def test_per_dim_scales_over_a_long_history_of_steps(D, kb, vb):
+    """More appended steps than the step tables of the dequantising mode hold (64): per-dim K scales are then folded
+    into the queries step by step, with key tiles cut at the step boundaries (one launch, no preparation)."""
+    fmt, B, H = "BLHc", 1, 2
+    steps = (1, 2, 3) * 22 + (40, 130)          # 68 steps, 302 tokens
+    kq, vq = VAR_Q(kb, fmt, "G_SCALE_HEAD_DIM", symmetric=False), VAR_Q(vb, fmt, "G_SCALE_HEAD_DIM")
+    kr, vr = O.OracleVARQ(kb, fmt, "G_SCALE_HEAD_DIM", symmetric=False), O.OracleVARQ(vb, fmt, "G_SCALE_HEAD_DIM")
+    for si, n in enumerate(steps):
+        k = O.synthetic_kv((B, n, H, D), fmt, 500 + si, n_outlier=4)
+        v = O.synthetic_kv((B, n, H, D), fmt, 700 + si, n_outlier=0)
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    q = torch.randn((B, 150, H, D), generator=torch.Generator().manual_seed(D))
+    scale = 1.0 / D ** 0.5
+    out, launches = run("tc", q.to(DEV), kq, vq, scale)
+    assert launches == 1
+    check(out, O.attention(q, kd, vd, fmt, scale), f"68 steps D={D}")

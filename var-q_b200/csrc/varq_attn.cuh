@@ -24,6 +24,12 @@ struct AttnArgs {
     long long prep_bh_stride = 0;
     int prep_tile_stride = 0, prep_off_vn = 0, prep_off_krec = 0, prep_off_vrec = 0;
     int prep_krec_bytes = 0, prep_vrec_bytes = 0;       // 0 = no records
+    // Per-dim parameters that the tokens of an appended step share: per (sample, head) a table [steps][3][D] of fp16
+    // (scale hi, scale lo, 1024 + bias + zero-point), and the records of a tile are then the step index of every key (uint16).
+    const unsigned char* prep_ktab = nullptr;
+    const unsigned char* prep_vtab = nullptr;
+    long long prep_tab_bh_stride = 0;               // bytes between the tables of two (sample, head) pairs
+    int tc_k_perdim = 0, tc_v_perdim = 0;
 };
 
 __device__ __forceinline__ float load_q_elem(const void* q, int dtype, long long off) {

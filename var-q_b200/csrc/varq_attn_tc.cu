@@ -677,6 +677,103 @@ __device__ __noinline__ void perdim_tile(unsigned char* tile, const uint32_t* pa
     }
 }
 
+// ---- per-dim parameters that the tokens of an appended step share, on regular key tiles: every key carries its step index
+// (uint16, staged with the tile) and the (sample, head) table [steps][3][D] of fp16 (scale hi, scale lo, 1024 + bias +
+// zero-point) is read through the read-only cache: neighbouring lanes convert neighbouring keys, which almost always belong
+// to the same step, so a load is one broadcast line.
+template <int HW> __device__ __forceinline__ void ldg_pairs(const __half* p, uint32_t (&r)[HW]) {
+    if constexpr (HW == 2) { const uint2 v = __ldg(reinterpret_cast<const uint2*>(p)); r[0] = v.x; r[1] = v.y; }
+    else {
+#pragma unroll
+        for (int i = 0; i < HW / 4; ++i) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+            r[4 * i] = v.x; r[4 * i + 1] = v.y; r[4 * i + 2] = v.z; r[4 * i + 3] = v.w;
+        }
+    }
+}
+// K: hi + lo operand tiles (128B-swizzled, K-major)
+template <int BITS>
+__device__ __noinline__ void perdim_split_tile(unsigned char* tile_hi, unsigned char* tile_lo, const uint32_t* packed, const uint16_t* step_of_key,
+                                               const __half* tab, int D, int n_valid, int N, int W, int ptid, int nthr) {
+    constexpr int VPW = 32 / BITS, HW = VPW / 2;
+    ItemWalk<true> wk;
+#pragma unroll 1
+    for (wk.init(ptid, N, W >> 2, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
+        const int d0 = wi * VPW;
+        uint32_t hi[4 * HW], lo[4 * HW];
+        if (key < n_valid) {
+            const uint4 pk = lds128(packed + key * W + wi);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            const __half* row = tab + (int)step_of_key[key] * 3 * D + d0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t d[HW], sh[HW], sl[HW], zb[HW];
+                Codes<BITS>::raw(wd[q], d);
+                ldg_pairs<HW>(row + q * VPW, sh);
+                ldg_pairs<HW>(row + D + q * VPW, sl);
+                ldg_pairs<HW>(row + 2 * D + q * VPW, zb);
+#pragma unroll
+                for (int c = 0; c < HW; ++c) {
+                    const uint32_t dz = h2_sub(d[c], zb[c]);
+                    const uint32_t h = h2_mul(dz, sh[c]);
+                    const uint32_t e = h2_fma(dz, sh[c], h ^ 0x80008000u);
+                    hi[q * HW + c] = h;
+                    lo[q * HW + c] = h2_fma(dz, sl[c], e);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) { hi[i] = 0u; lo[i] = 0u; }
+        }
+        const uint32_t rowo = (uint32_t)((d0 >> 6) * N * 128 + (key >> 3) * 1024 + (key & 7) * 128);
+        const int ch0 = (d0 & 63) >> 3;
+#pragma unroll
+        for (int c = 0; c < HW; ++c) {
+            const uint32_t off = rowo + (((ch0 + c) ^ (key & 7)) << 4);
+            sts128(tile_hi + off, hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+            sts128(tile_lo + off, lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
+        }
+    }
+}
+// V: one operand tile RN((code - zp) * scale) (unswizzled, MN-major; rows [n_valid, rows) zero-filled)
+template <int BITS>
+__device__ __noinline__ void perdim_steps_tile(unsigned char* tile, const uint32_t* packed, const uint16_t* step_of_key, const __half* tab, int D,
+                                               int n_valid, int N, int W, int ptid, int nthr, int rows) {
+    constexpr int VPW = 32 / BITS, HW = VPW / 2;
+    ItemWalk<true> wk;
+#pragma unroll 1
+    for (wk.init(ptid, rows, W >> 2, nthr); wk.more(); wk.next()) {
+        const int key = wk.key, wi = wk.item << 2;
+        const int d0 = wi * VPW;
+        uint32_t h[4 * HW];
+        if (key < n_valid) {
+            const uint4 pk = lds128(packed + key * W + wi);
+            const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+            const __half* row = tab + (int)step_of_key[key] * 3 * D + d0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t d[HW], sh[HW], sl[HW], zb[HW];
+                Codes<BITS>::raw(wd[q], d);
+                ldg_pairs<HW>(row + q * VPW, sh);
+                ldg_pairs<HW>(row + D + q * VPW, sl);
+                ldg_pairs<HW>(row + 2 * D + q * VPW, zb);
+#pragma unroll
+                for (int c = 0; c < HW; ++c) {
+                    const uint32_t dz = h2_sub(d[c], zb[c]);
+                    h[q * HW + c] = h2_fma(dz, sh[c], h2_mul(dz, sl[c]));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4 * HW; ++i) h[i] = 0u;
+        }
+        unsigned char* base = tile + vtile_off(key, d0, N);
+#pragma unroll
+        for (int c = 0; c < HW; ++c) sts128(base + c * (N * 16), h[4 * c], h[4 * c + 1], h[4 * c + 2], h[4 * c + 3]);
+    }
+}
+
 // ---- softmax over 32 columns of S held in registers.  Per-key tables (shared memory):
 // ks = K scale * softmax_scale * log2(e) (0 past the end), b2 = log2(folded V scale) (-1e30 past the
 // end), kzs = K zero-point * ks.
@@ -798,6 +895,9 @@ __device__ __noinline__ float new_reference(uint32_t s_addr, int nch, const floa
 //   normaliser      uint2 [N]         fp16 (hi, lo) of 2^-6 / V scale and of 2^-8 * V zero-point (1 and 0 when V is dequantised)
 //   K records       uint2 [N * groups] + 16-byte trailer     (only for the packed-half converter; see ParStage)
 //   V records       the same
+// Parameters that the tokens of an appended step share (per-dim scales): the records of a tile are the step index of every
+// key (uint16 [N] + trailer), and block 0 of every (sample, head) writes its table [steps][3][D] of fp16 (scale hi, scale lo,
+// 1024 + bias + zero-point) behind the tile blocks; every block scans the table's source for out-of-range parameters.
 template <int N>
 __global__ void __launch_bounds__(N) tc_prepare_kernel(AttnArgs a, int n_tiles, int k_split, int k_ng, int v_ng, int kb, int vb) {
     const int t = threadIdx.x;
@@ -862,8 +962,30 @@ __global__ void __launch_bounds__(N) tc_prepare_kernel(AttnArgs a, int n_tiles, 
         const int any_slow = __syncthreads_or(slow ? 1 : 0);
         if (t == 0) *reinterpret_cast<uint4*>(blk + off + N * ng * 8) = make_uint4((uint32_t)any_slow, 0u, 0u, 0u);
     };
-    records(a.kp, krow, k_ng, kb, a.prep_off_krec, a.prep_krec_bytes);
-    records(a.vp, vrow, v_ng, vb, a.prep_off_vrec, a.prep_vrec_bytes);
+    auto perdim = [&](const ParamView& pv, int row, int bits, int off, int bytes, const unsigned char* tab_base) {
+        reinterpret_cast<uint16_t*>(blk + off)[t] = (uint16_t)row;
+        const float bias = bits == 8 ? 128.f : bits == 4 ? 8.f : 2.f;
+        __half* tb = reinterpret_cast<__half*>(const_cast<unsigned char*>(tab_base) + (long long)bh * a.prep_tab_bh_stride);
+        bool slow = false;
+        for (int i = t; i < pv.n_rows * a.D; i += N) {
+            const int r = i / a.D, d = i - r * a.D;
+            const long long pi = pv.index(b, r, h, d);
+            const float sv = __ldg(pv.scale + pi), zv = pv.zp ? __ldg(pv.zp + pi) : 0.f;
+            slow = slow || !(fabsf(zv) <= 512.f) || !(sv < 60.f);
+            if (j == 0) {
+                const __half s_hi = __float2half_rn(sv);
+                tb[(r * 3 + 0) * a.D + d] = s_hi;
+                tb[(r * 3 + 1) * a.D + d] = __float2half_rn(sv - __half2float(s_hi));
+                tb[(r * 3 + 2) * a.D + d] = __float2half_rn(1024.f + bias + zv);
+            }
+        }
+        const int any_slow = __syncthreads_or(slow ? 1 : 0);
+        if (t == 0) *reinterpret_cast<uint4*>(blk + off + bytes - 16) = make_uint4((uint32_t)any_slow, 0u, 0u, 0u);
+    };
+    if (a.tc_k_perdim) perdim(a.kp, krow, kb, a.prep_off_krec, a.prep_krec_bytes, a.prep_ktab);
+    else records(a.kp, krow, k_ng, kb, a.prep_off_krec, a.prep_krec_bytes);
+    if (a.tc_v_perdim) perdim(a.vp, vrow, vb, a.prep_off_vrec, a.prep_vrec_bytes, a.prep_vtab);
+    else records(a.vp, vrow, v_ng, vb, a.prep_off_vrec, a.prep_vrec_bytes);
 }
 
 template <int D, int NQ, int KM>
@@ -1378,10 +1500,17 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                 const uint32_t* pk = reinterpret_cast<const uint32_t*>(smem + P::OFF_PK + (2 * s) * P::PK_BYTES);
                 unsigned char* tk = smem + P::OFF_K + s * P::KT * P::KV_BYTES;
                 if constexpr (KS) {
-                    const uint2* kpar = reinterpret_cast<const uint2*>(smem + (s ? P::OFF_KRAW : P::OFF_KPAR));
+                    const unsigned char* kst = smem + (s ? P::OFF_KRAW : P::OFF_KPAR);
+                    const uint2* kpar = reinterpret_cast<const uint2*>(kst);
                     // the trailer of the record block says whether a record of the tile is outside the packed-half converter's bounds
-                    const bool slow = !k_fast || reinterpret_cast<const uint32_t*>(kpar + (N << k_gshift))[0] != 0u;
-                    if (!slow) {
+                    const bool slow = !k_fast || *reinterpret_cast<const uint32_t*>(kst + a.prep_krec_bytes - 16) != 0u;
+                    if (!slow && a.tc_k_perdim) {
+                        const uint16_t* steps = reinterpret_cast<const uint16_t*>(kst);
+                        const __half* ktab = reinterpret_cast<const __half*>(a.prep_ktab + (long long)bh * a.prep_tab_bh_stride);
+                        if (kb == 8) perdim_split_tile<8>(tk, tk + P::KV_BYTES, pk, steps, ktab, D, n_valid, N, wk, ptid, KTHR);
+                        else if (kb == 4) perdim_split_tile<4>(tk, tk + P::KV_BYTES, pk, steps, ktab, D, n_valid, N, wk, ptid, KTHR);
+                        else perdim_split_tile<2>(tk, tk + P::KV_BYTES, pk, steps, ktab, D, n_valid, N, wk, ptid, KTHR);
+                    } else if (!slow) {
                         if (kb == 8) { if (k_fine) group_split_tile<8, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<8, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
                         else if (kb == 4) { if (k_fine) group_split_tile<4, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<4, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
                         else { if (k_fine) group_split_tile<2, 2>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); else group_split_tile<2, 4>(tk, tk + P::KV_BYTES, pk, kpar, n_valid, N, wk, ptid, KTHR, k_gshift, k_grp_shift); }
@@ -1569,9 +1698,16 @@ __global__ void __launch_bounds__(TcRoles<KM>::THREADS, 1) attn_tc_kernel(AttnAr
                     else if (vb == 4) codes_tile<4, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
                     else codes_tile<2, true>(tv, pv, n_valid, N, wv, ptid, VTHR, vrows);
                 } else {
-                    const uint2* vpar = reinterpret_cast<const uint2*>(smem + (s ? P::OFF_VRAW : P::OFF_VPAR));
-                    const bool slow = !v_grouped || reinterpret_cast<const uint32_t*>(vpar + (N << v_gshift))[0] != 0u;
-                    if (!slow) {
+                    const unsigned char* vst = smem + (s ? P::OFF_VRAW : P::OFF_VPAR);
+                    const uint2* vpar = reinterpret_cast<const uint2*>(vst);
+                    const bool slow = !v_grouped || *reinterpret_cast<const uint32_t*>(vst + a.prep_vrec_bytes - 16) != 0u;
+                    if (!slow && a.tc_v_perdim) {
+                        const uint16_t* steps = reinterpret_cast<const uint16_t*>(vst);
+                        const __half* vtab = reinterpret_cast<const __half*>(a.prep_vtab + (long long)bh * a.prep_tab_bh_stride);
+                        if (vb == 8) perdim_steps_tile<8>(tv, pv, steps, vtab, D, n_valid, N, wv, ptid, VTHR, vrows);
+                        else if (vb == 4) perdim_steps_tile<4>(tv, pv, steps, vtab, D, n_valid, N, wv, ptid, VTHR, vrows);
+                        else perdim_steps_tile<2>(tv, pv, steps, vtab, D, n_valid, N, wv, ptid, VTHR, vrows);
+                    } else if (!slow) {
                         if (vb == 8) { if (v_fine) group_tile<8, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<8, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
                         else if (vb == 4) { if (v_fine) group_tile<4, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<4, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
                         else { if (v_fine) group_tile<2, 2>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); else group_tile<2, 4>(tv, pv, vpar, n_valid, N, wv, ptid, VTHR, vrows, v_gshift, v_grp_shift); }
@@ -1748,12 +1884,19 @@ static bool records_apply(int group, int D, int bits, int N) {
     return group != D && (group % vpw) == 0 && (group & (group - 1)) == 0 && N * ng <= 256;
 }
 static size_t prep_tile_bytes_max(int N) { return (size_t)3 * N * 4 + (size_t)N * 8 + 2 * (256 * 8 + 16); }
+// Per-dim parameters shared by the tokens of a step are served from per-(sample, head) tables of at most this many steps
+// (the schedules of the models have 10 to 13); longer histories take the folded-query kernel.
+constexpr int TC_MAX_STEPS = 64;
+static bool steps_apply(const ParamView& pv, int D, int bits) {
+    return pv.group != D && pv.row_of_token != nullptr && pv.n_rows > 0 && pv.n_rows <= TC_MAX_STEPS && (D % (4 * (32 / bits))) == 0;
+}
 
 size_t attn_tc_workspace_bytes(int B, int H, int Lk, int D) {
     if (D != 64 && D != 128) return 0;
     const int N = D == 64 ? 128 : 64;
     const size_t tiles = (size_t)(Lk + N - 1) / N;
-    return (size_t)B * H * tiles * prep_tile_bytes_max(N) + 256;       // + room to align the base
+    const size_t tables = (size_t)2 * TC_MAX_STEPS * 3 * D * 2;       // K and V step tables of one (sample, head)
+    return (size_t)B * H * (tiles * prep_tile_bytes_max(N) + tables) + 256;       // + room to align the base
 }
 
 template <int D, int NQ, int KM>
@@ -1763,21 +1906,28 @@ static int launch_tc(const AttnArgs& a0, int kb, int vb, void* ws, size_t ws_byt
     if constexpr (KM != KM_FOLD) {
         constexpr int N = P::N;
         const int T = (a.Lk + N - 1) / N;
-        const bool k_rec = KM == KM_SPLIT && records_apply(a.kp.group, D, kb, N);
-        const bool v_rec = records_apply(a.vp.group, D, vb, N);
+        a.tc_k_perdim = KM == KM_SPLIT && steps_apply(a.kp, D, kb);
+        a.tc_v_perdim = steps_apply(a.vp, D, vb);
+        const bool k_rec = KM == KM_SPLIT && !a.tc_k_perdim && records_apply(a.kp.group, D, kb, N);
+        const bool v_rec = !a.tc_v_perdim && records_apply(a.vp.group, D, vb, N);
         const int k_ng = D / a.kp.group, v_ng = D / a.vp.group;
         a.prep_off_vn = P::TAB_ROWS * N * 4;
         a.prep_off_krec = a.prep_off_vn + N * 8;
-        a.prep_krec_bytes = k_rec ? N * k_ng * 8 + 16 : 0;
+        a.prep_krec_bytes = a.tc_k_perdim ? N * 2 + 16 : k_rec ? N * k_ng * 8 + 16 : 0;
         a.prep_off_vrec = a.prep_off_krec + a.prep_krec_bytes;
-        a.prep_vrec_bytes = v_rec ? N * v_ng * 8 + 16 : 0;
+        a.prep_vrec_bytes = a.tc_v_perdim ? N * 2 + 16 : v_rec ? N * v_ng * 8 + 16 : 0;
         a.prep_tile_stride = a.prep_off_vrec + a.prep_vrec_bytes;
         a.prep_bh_stride = (long long)T * a.prep_tile_stride;
+        const int tab_k = a.tc_k_perdim ? a.kp.n_rows * 3 * D * 2 : 0, tab_v = a.tc_v_perdim ? a.vp.n_rows * 3 * D * 2 : 0;
+        a.prep_tab_bh_stride = tab_k + tab_v;
         const uintptr_t base = (reinterpret_cast<uintptr_t>(ws) + 255) & ~(uintptr_t)255;
-        const size_t need = (size_t)a.B * a.H * (size_t)a.prep_bh_stride + (base - reinterpret_cast<uintptr_t>(ws));
+        const size_t tiles_bytes = (size_t)a.B * a.H * (size_t)a.prep_bh_stride;
+        const size_t need = tiles_bytes + (size_t)a.B * a.H * (size_t)a.prep_tab_bh_stride + (base - reinterpret_cast<uintptr_t>(ws));
         if (!ws || ws_bytes < need)
             return fail(VARQ_ERR_WORKSPACE, "varq_attn_fwd: workspace of %zu bytes needed, %zu given", need, ws_bytes);
         a.prep = reinterpret_cast<unsigned char*>(base);
+        a.prep_ktab = a.prep + tiles_bytes;          // tile blocks are multiples of 16 bytes, and so are the tables
+        a.prep_vtab = a.prep_ktab + tab_k;
         const long long prep_blocks = (long long)a.B * a.H * T;
         if (prep_blocks > 0x7fffffffLL) return fail(VARQ_ERR_UNSUPPORTED, "varq_attn_fwd: more than 2^31 thread blocks");
         tc_prepare_kernel<N><<<(unsigned)prep_blocks, N, 0, st>>>(a, T, KM == KM_SPLIT ? 1 : 0, k_ng, v_ng, kb, vb);
@@ -1810,8 +1960,9 @@ int attn_tc_run(const AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cu
     const bool varies = a.kp.group != a.D;         // K scale varies along head_dim
     // ... but is constant over the tokens of a step, the steps are known, and their tile schedule fits: fold it into Q
     const int n_max = a.D == 64 ? 128 : 64;
-    const bool fold = varies && a.kp.row_of_token && a.kp.row_begin && a.kp.n_rows > 0 && a.kp.n_rows <= 0xffff &&
-                      (a.Lk + n_max - 1) / n_max + a.kp.n_rows <= TC_MAX_TILES;
+    // (only for histories of more steps than the step tables of the dequantising mode hold)
+    const bool fold = varies && !steps_apply(a.kp, a.D, kb) && a.kp.row_of_token && a.kp.row_begin && a.kp.n_rows > 0 &&
+                      a.kp.n_rows <= 0xffff && (a.Lk + n_max - 1) / n_max + a.kp.n_rows <= TC_MAX_TILES;
     if (a.D == 64) {
         if (fold) return launch_tc<64, 2, KM_FOLD>(a, kb, vb, ws, ws_bytes, st);
         if (varies) return split_q ? launch_tc<64, 2, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st) : launch_tc<64, 1, KM_SPLIT>(a, kb, vb, ws, ws_bytes, st);
