@@ -20,8 +20,11 @@
 //              (O_half | normaliser sums) += P (V | normaliser columns), so the tensor core adds up exactly the rounded P that
 //              it multiplies with V, and commits completion to mbarriers;
 //   copy warp  one thread requests tile t + 2 of each stream as soon as the converters have arrived for tile t.
-// In the folded-query mode (per-dim K scales that are constant over the tokens of an appended step) the older arrangement is
-// kept: 4 + 3 producer warps that also fetch parameters, write the tables and request their own copies, and no copy warp.
+// Per-dim scales that the tokens of an appended step share (the reference's shipped mode) take the dequantising converters
+// with a per-(sample, head) table of the steps' parameters and a step index per key.  Only histories of more steps than
+// those tables hold fall back to the folded-query mode (Q * s(step) rewritten per step, key tiles cut at step boundaries),
+// which keeps the older arrangement: 4 + 3 producer warps that also fetch parameters, write the tables and request their
+// own copies, and no copy warp.
 // Numerics: integer codes are exact in fp16 and the K scale is applied to S in fp32, so QK^T has
 // no rounding beyond Q's; an fp32 Q is split into hi + lo fp16 halves (two MMAs).  P and V are
 // rounded to fp16 (bf16 would miss the 1e-3 relative-L2 target by 10x).  A V scale below 2^-20
@@ -207,7 +210,8 @@ __device__ __forceinline__ uint32_t tile_off(int row, int col, int rows) {
 // ---------------------------------------------------------------- shared-memory plan
 // How K reaches the tensor core:
 //   KM_EXACT  integer codes; one scale / zero-point per key, applied to S in fp32
-//   KM_SPLIT  (code - zp) * scale as an fp16 hi + lo pair of operand tiles, for scales that vary along head_dim per key
+//   KM_SPLIT  (code - zp) * scale as an fp16 hi + lo pair of operand tiles, for scales that vary along head_dim: per key
+//             (group-wise records) or per appended step (step tables)
 //   KM_FOLD   integer codes; scales that vary along head_dim but are constant over the tokens of an appended step are
 //             folded into the queries (Q * s as fp16 hi + lo, rewritten when a key tile starts a new step), the
 //             zero-point term sum_d q_d s_d z_d is a per-row constant taken off S; key tiles end at step boundaries
