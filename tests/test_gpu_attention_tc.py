@@ -193,3 +193,63 @@ def test_per_dim_scales_over_a_long_history_of_steps(D, kb, vb):
     out, launches = run("tc", q.to(DEV), kq, vq, scale)
     assert launches == 1
     check(out, O.attention(q, kd, vd, fmt, scale), f"68 steps D={D}")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("kkw,vkw", [
+    (dict(mode="G_TOKEN_HEAD", symmetric=False, group_size=32), dict(mode="G_TOKEN_HEAD", symmetric=False, group_size=32)),
+    (dict(mode="G_SCALE_HEAD_DIM", symmetric=False), dict(mode="G_SCALE_HEAD_DIM", symmetric=False)),
+])
+def test_parameters_outside_the_packed_half_converters_bounds(D, kkw, vkw):
+    """K values far from zero with a narrow range give zero-points below -512; V scaled up gives scales above 60: the
+    preparation kernel flags such tiles and the converters take their fp32 routine (first step only: the second one is
+    ordinary data, so flagged and unflagged tiles alternate inside one launch where the parameters are per key)."""
+    fmt, B, H = "BLHc", 2, 2
+    kkw, vkw = dict(kkw), dict(vkw)
+    km, vm = kkw.pop("mode"), vkw.pop("mode")
+    kq, vq = VAR_Q(4, fmt, km, **kkw), VAR_Q(4, fmt, vm, **vkw)
+    kr, vr = O.OracleVARQ(4, fmt, km, **kkw), O.OracleVARQ(4, fmt, vm, **vkw)
+    for si, n in enumerate((200, 150)):
+        k = O.synthetic_kv((B, n, H, D), fmt, 900 + si, n_outlier=0)
+        v = O.synthetic_kv((B, n, H, D), fmt, 950 + si, n_outlier=0)
+        if si == 0:
+            k = 5.0 + 0.01 * k            # zero-point = round(-8 - min / scale) is about -1250
+            v = 1000.0 * v                # scale = range / 15 is about 500
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    assert kq._zp_tbl[:, :, :kq._n_rows].abs().max().item() > 512 and vq._scale_tbl[:, :, :vq._n_rows].max().item() > 60
+    q = torch.randn((B, 130, H, D), generator=torch.Generator().manual_seed(D))
+    scale = 1.0 / D ** 0.5
+    out, _ = run("tc", q.to(DEV), kq, vq, scale)
+    ref = O.attention(q, kd, vd, fmt, scale)
+    out, ref = out.float().cpu(), ref.float().cpu()
+    rel = ((out - ref).norm() / ref.norm()).item()
+    # the outputs are of the order of V (hundreds): the absolute bound scales with them
+    assert rel <= 1e-3 and (out - ref).abs().max().item() <= 2e-3 * max(1.0, ref.abs().max().item()), f"rel-L2 {rel:.3e}"
+
+
+def test_tensor_core_path_refuses_a_missing_workspace():
+    """The preparation streams live in the caller's workspace: without one the call fails with VARQ_ERR_WORKSPACE and
+    launches nothing."""
+    fmt, B, H, D, lq, lk = "BLHc", 1, 2, 64, 40, 100
+    kq, vq = VAR_Q(8, fmt, "G_TOKEN_HEAD"), VAR_Q(8, fmt, "G_TOKEN_HEAD")
+    kq.append(torch.randn(B, lk, H, D, device=DEV)); vq.append(torch.randn(B, lk, H, D, device=DEV))
+    q = torch.randn(B, lq, H, D, device=DEV)
+    out = torch.empty(B, lq, H, D, device=DEV)
+    lib = _cabi.lib()
+    kc, kp = kq.cache_descriptors()
+    vc, vp = vq.cache_descriptors()
+    qd = kq._item_desc(q)
+    od = _cabi.tensor_desc(out.data_ptr(), _cabi.F32, lq * H * D, H * D, D)
+    need = lib.varq_attn_workspace_bytes(B, H, lq, lk, D, 8, 8)
+    assert need > 0
+    _cabi.force_attn_path("tc")
+    n0 = lib.varq_launch_count()
+    rc = lib.varq_attn_fwd(qd, kc, vc, kp, vp, B, H, lq, lk, D, 8, 8, 0.125, od, None, 0, _cabi.stream_ptr(q.device))
+    assert rc == -4 and b"workspace" in lib.varq_last_error()
+    assert lib.varq_launch_count() == n0
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    rc = lib.varq_attn_fwd(qd, kc, vc, kp, vp, B, H, lq, lk, D, 8, 8, 0.125, od, ws.data_ptr(), need, _cabi.stream_ptr(q.device))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == 0 and torch.isfinite(out).all()
