@@ -193,6 +193,7 @@ int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_t L, int32_
 #define VARQ_ATTN_PATH_SMALL  1
 #define VARQ_ATTN_PATH_STREAM 2
 #define VARQ_ATTN_PATH_TC     3
+#define VARQ_ATTN_PATH_MID    4
 int varq_attn_force_path(int32_t path);
 
 /* Bytes of scratch varq_attn_fwd needs for this shape, whichever kernel it picks: partial results of the

@@ -138,7 +138,7 @@ def _attn_call(path, q, kq, vq, scale, out_dtype):
     return out.payload.view(B, Lq, H, D), lib.varq_launch_count() - n0
 
 
-@pytest.mark.parametrize("path", ["small", "stream", "tc"])
+@pytest.mark.parametrize("path", ["small", "stream", "tc", "mid"])
 @pytest.mark.parametrize("D,kb,vb", [(64, 8, 4), (128, 4, 2)])
 @pytest.mark.parametrize("lq,lk", [(1, 1), (1, 333), (3, 129), (16, 2047), (17, 65), (130, 131), (257, 1000)])
 def test_attention_kernels_stay_inside_their_buffers(path, D, kb, vb, lq, lk):

@@ -139,11 +139,11 @@ def workspace(device, nbytes: int) -> torch.Tensor:
     return buf
 
 
-ATTN_PATHS = {None: 0, "auto": 0, "small": 1, "stream": 2, "tc": 3}
+ATTN_PATHS = {None: 0, "auto": 0, "small": 1, "stream": 2, "tc": 3, "mid": 4}
 
 
 def force_attn_path(name):
-    """Pin the attention kernel for later calls ("small", "stream", "tc"; None = automatic).  Test hook."""
+    """Pin the attention kernel for later calls ("small", "stream", "tc", "mid"; None = automatic).  Test hook."""
     check(lib().varq_attn_force_path(ATTN_PATHS[name]))
 
 

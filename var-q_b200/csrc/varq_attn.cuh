@@ -107,5 +107,7 @@ bool attn_tc_eligible(const AttnArgs& a, int kb, int vb);
 int attn_tc_run(const AttnArgs& a, int kb, int vb, void* ws, size_t ws_bytes, cudaStream_t st);
 size_t attn_tc_workspace_bytes(int B, int H, int Lk, int D);
 int attn_tc_status(int* out);
+bool attn_mid_eligible(const AttnArgs& a, int kb, int vb);
+int attn_mid_run(AttnArgs& a, int kb, int vb, cudaStream_t st);
 
 }  // namespace varq

@@ -63,6 +63,11 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
     // 128-row tile with few live rows still finishes a long cache sooner.
     const int force = __atomic_load_n(&g_forced_path, __ATOMIC_RELAXED);
     const bool small_q = Lq <= 4 || (Lq <= 16 && Lk <= 256);
+    // Between the two: tens of queries over at most a few hundred tokens (the early scales of a schedule), where the tcgen05
+    // kernel is bound by its per-CTA set-up; a warp-level tensor-core kernel takes them when the parameters are per key.
+    const bool mid_q = Lq > 8 && Lq <= 64 && Lk <= 256;          // measured against both neighbours (B64 H16 and B128 H30, c 64)
+    const bool want_mid = force ? (force == VARQ_ATTN_PATH_MID) : mid_q;
+    if (want_mid && attn_mid_eligible(a, kb, vb)) return attn_mid_run(a, kb, vb, (cudaStream_t)stream);
     const bool want_tc = force ? (force == VARQ_ATTN_PATH_TC) : !small_q;
     if (want_tc && attn_tc_eligible(a, kb, vb)) return attn_tc_run(a, kb, vb, workspace, workspace_bytes, (cudaStream_t)stream);
     const bool want_stream = force ? (force == VARQ_ATTN_PATH_STREAM) : small_q;
@@ -71,7 +76,7 @@ extern "C" int varq_attn_fwd(const varq_tensor_t* q, const varq_tensor_t* k_code
 }
 
 extern "C" int varq_attn_force_path(int32_t path) {
-    if (path < VARQ_ATTN_PATH_AUTO || path > VARQ_ATTN_PATH_TC) return fail(VARQ_ERR_ARG, "varq_attn_force_path: unknown path %d", path);
+    if (path < VARQ_ATTN_PATH_AUTO || path > VARQ_ATTN_PATH_MID) return fail(VARQ_ERR_ARG, "varq_attn_force_path: unknown path %d", path);
     __atomic_store_n(&g_forced_path, (int)path, __ATOMIC_RELAXED);
     return VARQ_OK;
 }
