@@ -351,12 +351,15 @@ def kernel_rooflines(device, peaks):
     g32 = lambda b: (b, "G_TOKEN_HEAD", dict(symmetric=False, group_size=32))
     attn_case("attention, streaming CUDA-core kernel (group-32 INT4 K / INT2 V)", 64, 16, 128, 1, 10521, g32(4), g32(2), torch.bfloat16)
     attn_case("attention, streaming CUDA-core kernel, 16 queries (per-head INT8)", 64, 16, 128, 16, 10521, ph8, ph8, torch.bfloat16)
+    attn_case("attention, warp-level tensor-core kernel for the early scales (per-head INT8)", 64, 16, 64, 25, 55, ph8, ph8, torch.float32, fmt="BLHc", reps=20)
     attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 64, 16, 64, 256, 680, ph8, ph8, torch.float32, fmt="BLHc", reps=20)
     attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 64, 16, 64, 1024, 2240, ph8, ph8, torch.bfloat16, fmt="BLHc")
     attn_case("attention, tensor-core kernel, exact-code K (per-head INT8)", 16, 16, 128, 4096, 10521, ph8, ph8, torch.bfloat16)
     attn_case("attention, tensor-core kernel, per-dim K (asymmetric INT4 K per-dim, V per-head)", 64, 16, 64, 1024, 2240,
               (4, "G_SCALE_HEAD_DIM", dict(symmetric=False)), (4, "G_TOKEN_HEAD", dict(symmetric=False)), torch.float32, fmt="BLHc")
     attn_case("attention, tensor-core kernel, group-wise K and V (INT4 K / INT2 V, group 32)", 16, 16, 128, 4096, 10521, g32(4), g32(2), torch.float32)
+    pd8 = (8, "G_SCALE_HEAD_DIM", {})
+    attn_case("attention, tensor-core kernel, per-dim INT8 K and V (the reference's shipped mode)", 64, 16, 64, 1024, 2240, pd8, pd8, torch.float32, fmt="BLHc")
     return recs
 
 
@@ -857,10 +860,13 @@ def run_case(name):
     g = torch.Generator(device=dev).manual_seed(0)
     nbytes = None
     if name.startswith("attn"):
-        # attn: the VAR-d16 last scale at a quarter of the batch (exact-code K); attn_perdim: VAR-d30 K/V settings, Lq 1024 over
+        # attn: the VAR-d16 last scale at a quarter of the batch (exact-code K); attn_early: one of its early scales; attn_perdim: VAR-d30 K/V settings, Lq 1024 over
         # 2240 tokens in ten steps, 8 samples; attn_group: Infinity settings, Lq 1024 over 4096 tokens, 4 samples
         if name == "attn":
             B, H, D, fmt, steps, lq = 16, 16, 64, "BLHc", (680,), 256
+            ka, va = (8, "G_TOKEN_HEAD", {}), (8, "G_TOKEN_HEAD", {})
+        elif name == "attn_early":      # the fifth scale of the VAR-d16 schedule at full batch: 25 queries over 55 cached tokens
+            B, H, D, fmt, steps, lq = 64, 16, 64, "BLHc", (1, 4, 9, 16, 25), 25
             ka, va = (8, "G_TOKEN_HEAD", {}), (8, "G_TOKEN_HEAD", {})
         elif name == "attn_perdim":
             B, H, D, fmt, steps, lq = 8, 30, 64, "BLHc", WORKLOADS["var_d30"]["steps_l"], 1024
@@ -911,7 +917,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the isolated dequant-attention sweep")
     ap.add_argument("--quick", action="store_true", help="headline measurement only (no per-kernel rooflines, sweep, other workloads, CPU leg)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--case", choices=("attn", "attn_perdim", "attn_group", "stream", "quant", "quant2"),
+    ap.add_argument("--case", choices=("attn", "attn_early", "attn_perdim", "attn_group", "stream", "quant", "quant2"),
                     help="run one kernel on a small case and exit (profiling aid)")
     args = ap.parse_args()
     if args.case:

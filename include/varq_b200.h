@@ -186,8 +186,9 @@ int varq_unpack_dequant(const varq_tensor_t* codes, int32_t B, int32_t L, int32_
                         const varq_tensor_t* out, void* stream);
 
 /* Pin the kernel varq_attn_fwd uses for every later call of the process: automatic choice, the general
- * CUDA-core kernel, the streaming CUDA-core kernel or the tensor-core kernel.  A pinned kernel that cannot take
- * a call (shape, layout) yields to the general kernel.  For tests and measurements that compare the kernels on
+ * CUDA-core kernel, the streaming CUDA-core kernel, the tcgen05 tensor-core kernel or the warp-level tensor-core
+ * kernel of the early scales (MID).  A pinned kernel that cannot take a call (shape, layout, grouping) yields to the
+ * next one in the automatic order and finally to the general kernel.  For tests and measurements that compare the kernels on
  * one input; no counterpart in the reference. */
 #define VARQ_ATTN_PATH_AUTO   0
 #define VARQ_ATTN_PATH_SMALL  1
