@@ -90,3 +90,23 @@ def test_other_groupings_go_elsewhere():
     q = torch.randn((1, 40, 2, 64), generator=torch.Generator().manual_seed(9))
     out, _ = run(q.to(DEV), kq, vq, 0.125)
     check(out, O.attention(q, kd, vd, "BLHc", 0.125), "group 32")
+
+
+@pytest.mark.parametrize("gain", [1e-3, 3e4])
+def test_v_scales_far_from_one(gain):
+    """The V scale is folded into the softmax weights through the exponent, so the fp16 operand stays normalised for
+    small and for huge V values alike (scales below 2^-20 are folded as 2^-20, like in the tcgen05 kernel); the result is
+    compared relative to its own magnitude."""
+    kq, vq = VAR_Q(8, "BLHc", "G_TOKEN_HEAD"), VAR_Q(8, "BLHc", "G_TOKEN_HEAD", symmetric=False)
+    kr, vr = O.OracleVARQ(8, "BLHc", "G_TOKEN_HEAD"), O.OracleVARQ(8, "BLHc", "G_TOKEN_HEAD", symmetric=False)
+    for si, n in enumerate((40, 60)):
+        k = O.synthetic_kv((2, n, 2, 64), "BLHc", 11 + si, n_outlier=4)
+        v = gain * O.synthetic_kv((2, n, 2, 64), "BLHc", 21 + si, n_outlier=0)
+        kq.append(k.to(DEV)); vq.append(v.to(DEV))
+        kd, vd = kr.use_var_q(k), vr.use_var_q(v)
+    q = torch.randn((2, 30, 2, 64), generator=torch.Generator().manual_seed(4))
+    out, _ = run(q.to(DEV), kq, vq, 0.125)
+    ref = O.attention(q, kd, vd, "BLHc", 0.125)
+    out = out.float().cpu()
+    assert (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    assert ((out - ref).norm() / ref.norm()).item() <= 1e-3

@@ -8,7 +8,7 @@
 // One CTA = one (sample, head) x 32 or 64 queries, two or four warps of 16 query rows.  Keys go through shared memory 64 at a time:
 // the packed rows are turned into exact fp16 integer codes (byte permutes), S = Q K^T on codes, the per-key K scale and
 // zero-point are applied to S in fp32 (s_k * (acc - z_k * sum q)), online softmax in registers (base 2), the per-key V scale is
-// folded into P before it is rounded to fp16, O += P V on codes, and the V zero-point term sum_k P_k z_k is subtracted at the
+// folded into P through the exponent before it is rounded to fp16 (and divided out of the normaliser), O += P V on codes, and the V zero-point term sum_k P_k z_k is subtracted at the
 // end.  An fp32 query is split into fp16 hi + lo operands (two MMAs), like in the tcgen05 kernel.  Only groupings with one
 // scale / zero-point per key (per token, per token and head, per appended step) and head_dim 64 are taken.
 #include <cfloat>
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(WARPS * 32, (QSPLIT ? 12 : 16) / WARPS) attn_m
     constexpr int NQ = QSPLIT ? 2 : 1;
     __shared__ __align__(16) __half sK[MID_KEYS * PITCH];
     __shared__ __align__(16) __half sV[MID_KEYS * PITCH];
-    __shared__ float sKs[MID_KEYS], sKz[MID_KEYS], sVs[MID_KEYS], sVz[MID_KEYS];
+    __shared__ float sKs[MID_KEYS], sKz[MID_KEYS], sVs[MID_KEYS], sVr[MID_KEYS], sVz[MID_KEYS];    // sVs = log2 (V scale), sVr = 1 / (V scale)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int qt = (int)(blockIdx.x % (unsigned)a.n_qtiles), bh = (int)(blockIdx.x / (unsigned)a.n_qtiles), b = bh / a.H, h = bh - b * a.H;
@@ -209,10 +209,11 @@ __global__ void __launch_bounds__(WARPS * 32, (QSPLIT ? 12 : 16) / WARPS) attn_m
                 const long long pk = a.kp.index(b, a.kp.row(key), h, 0), pv = a.vp.index(b, a.vp.row(key), h, 0);
                 ks = __ldg(a.kp.scale + pk) * a.scale_log2;
                 if (kz_on) kz = __ldg(a.kp.zp + pk) * ks;
-                vs = __ldg(a.vp.scale + pv);
+                vs = fmaxf(__ldg(a.vp.scale + pv), 9.5367431640625e-07f);      // a V scale below 2^-20 is folded as 2^-20
                 if (vz_on) vz = __ldg(a.vp.zp + pv);
             }
-            sKs[tid] = ks; sKz[tid] = kz; sVs[tid] = vs; sVz[tid] = vz;
+            // the V scale enters the exponent (P stays normalised in fp16 whatever its magnitude) and leaves the normaliser again
+            sKs[tid] = ks; sKz[tid] = kz; sVs[tid] = key < a.Lk ? __log2f(vs) : 0.f; sVr[tid] = key < a.Lk ? __frcp_rn(vs) : 0.f; sVz[tid] = vz;
         }
         __syncthreads();
         if (!warp_live) continue;
@@ -246,9 +247,9 @@ __global__ void __launch_bounds__(WARPS * 32, (QSPLIT ? 12 : 16) / WARPS) attn_m
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const bool live = k0 + kc + e < a.Lk;
-                const float ks = sKs[kc + e], kz = sKz[kc + e];
-                s[j][e] = live ? fmaf(s[j][e], ks, -kz * qsum0) : -1e30f;
-                s[j][2 + e] = live ? fmaf(s[j][2 + e], ks, -kz * qsum1) : -1e30f;
+                const float ks = sKs[kc + e], kz = sKz[kc + e], lv = sVs[kc + e];
+                s[j][e] = live ? fmaf(s[j][e], ks, fmaf(-kz, qsum0, lv)) : -1e30f;
+                s[j][2 + e] = live ? fmaf(s[j][2 + e], ks, fmaf(-kz, qsum1, lv)) : -1e30f;
                 mx0 = fmaxf(mx0, s[j][e]);
                 mx1 = fmaxf(mx1, s[j][2 + e]);
             }
@@ -266,11 +267,12 @@ __global__ void __launch_bounds__(WARPS * 32, (QSPLIT ? 12 : 16) / WARPS) attn_m
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int kc = j * 8 + cq;
-            const float vs_a = sVs[kc], vs_b = sVs[kc + 1], vz_a = sVz[kc], vz_b = sVz[kc + 1];
-            const float p00 = mid_ex2(s[j][0] - m0), p01 = mid_ex2(s[j][1] - m0);
+            const float vr_a = sVr[kc], vr_b = sVr[kc + 1], vz_a = sVz[kc], vz_b = sVz[kc + 1];
+            const float p00 = mid_ex2(s[j][0] - m0), p01 = mid_ex2(s[j][1] - m0);      // = softmax weight x V scale, at most 1
             const float p10 = mid_ex2(s[j][2] - m1), p11 = mid_ex2(s[j][3] - m1);
-            l0 += p00 + p01; l1 += p10 + p11;
-            const __half2 h0 = __floats2half2_rn(p00 * vs_a, p01 * vs_b), h1 = __floats2half2_rn(p10 * vs_a, p11 * vs_b);
+            l0 = fmaf(p00, vr_a, fmaf(p01, vr_b, l0));
+            l1 = fmaf(p10, vr_a, fmaf(p11, vr_b, l1));
+            const __half2 h0 = __floats2half2_rn(p00, p01), h1 = __floats2half2_rn(p10, p11);
             const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);     // the zero-point term uses the rounded P
             cz0 = fmaf(f0.x, vz_a, fmaf(f0.y, vz_b, cz0));
             cz1 = fmaf(f1.x, vz_a, fmaf(f1.y, vz_b, cz1));
